@@ -1,0 +1,400 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE all-to-all path: dispatch + expert placeholder + combine.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c4]
+
+One process per GPU (N > 1: launched by ``python -m torch.distributed.run``; rank,
+world size and rendezvous come from the environment).  A step is one
+``custom_kernel`` forward of every rank on the 256-expert / top-8 / hidden 7168 /
+256 tokens-per-rank bf16 workload with the experts split evenly over the N ranks.
+Rank 0 prints ONE JSON line.
+
+Timed region (``value``): inputs resident in HBM; per step an untimed L2 flush
+(256 MiB write) and, for N > 1, a device-side rendezvous of all ranks, then CUDA
+events on the launching stream around the forward; a step costs the maximum over
+ranks; the K steps are enqueued back to back with a synchronise and barrier on
+both sides of the loop.  ``e2e`` times the same step through the host-buffer entry
+point (pinned host tensors in, pinned host tensor out, copies inside the events).
+``--impl reference`` times the CPU restatement of the reference's Python path
+(oracle/, gloo, one process per rank on the host cores).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "dispatch+combine us (max over ranks)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c4")
+    ap.add_argument("--payload", default=None, help="direct | dedup | fp8 (default: the workload's own)")
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed loop runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _names(self, mask: int):
+        nv = self.nv
+        table = {
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "hw_power_brake": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        return [n for n, bit in table.items() if mask & bit]
+
+    def _run(self):
+        nv = self.nv
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                if get_reasons is not None:
+                    self.reasons.update(self._names(int(get_reasons(self.h))))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(1.0)
+
+    def summary(self):
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:  # noqa: BLE001
+            return local_index
+    return local_index
+
+
+# ---------------------------------------------------------------------------
+# reference arm: the CPU restatement of the reference's Python path, under gloo
+# ---------------------------------------------------------------------------
+def _ref_rank(rank, ws, port, workload, steps, warmup, threads, q):
+    import torch.distributed as dist
+
+    import gpu_mode_kernels_b200 as pkg
+    from oracle import a2a_oracle as O
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(threads)
+    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    cfg, rd, _, _ = pkg.workload_input(workload, rank, ws)
+    ata = O.PortAllToAll(cfg, rank, ws)
+    full_tokens = rd.num_tokens
+    budget_s = float(os.environ.get("A2A_REFERENCE_BUDGET_S", "150"))
+
+    def one_step(n_tok):
+        x, idx, w = rd.x[:n_tok], rd.indices[:n_tok], rd.weights[:n_tok]
+        dist.barrier()
+        t0 = time.perf_counter()
+        n, ex, em = ata.dispatch(x, idx)
+        t1 = time.perf_counter()
+        ey = O.port_expert_op(ex, cfg.out_dtype, rank, n)  # valid rows only; not part of the metric
+        t2 = time.perf_counter()
+        y = torch.zeros(cfg.max_num_tokens, cfg.hidden_dim, dtype=cfg.out_dtype)
+        ata.combine(y, w, em, ey, n)
+        t3 = time.perf_counter()
+        t = torch.tensor([(t1 - t0) + (t3 - t2), t2 - t1], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]), float(t[1])
+
+    # One full-size probe step decides whether the steps can be full size within the
+    # time budget; if not, every step runs on the first n_tok tokens of each rank and
+    # its time is scaled by full_tokens / n_tok (the Python loops are linear in tokens).
+    probe, _ = one_step(full_tokens)
+    n_tok = full_tokens
+    if probe * (steps + warmup) > budget_s:
+        n_tok = max(8, int(full_tokens * budget_s / (probe * (steps + warmup))))
+    scale = full_tokens / n_tok
+    times, expert_s = [], []
+    for it in range(warmup + steps):
+        a, b = one_step(n_tok)
+        if it >= warmup:
+            times.append(a * scale)
+            expert_s.append(b * scale)
+    if rank == 0:
+        q.put((times, expert_s, n_tok, full_tokens))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def run_reference_cpu(ws: int, workload: str, steps: int, warmup: int):
+    """dispatch+combine seconds per step (max over CPU ranks) of the port; all host threads."""
+    import torch.multiprocessing as mp
+
+    cores = os.cpu_count() or 1
+    threads = max(1, cores // ws)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29900 + (os.getpid() % 50)
+    procs = [ctx.Process(target=_ref_rank, args=(r, ws, port, workload, steps, warmup, threads, q)) for r in range(ws)]
+    for p in procs:
+        p.start()
+    times, expert_s, n_tok, full_tokens = q.get(timeout=3600)
+    for p in procs:
+        p.join(120)
+    return times, expert_s, cores, threads, (n_tok, full_tokens)
+
+
+def reference_main(args, rank: int, ws: int):
+    if rank != 0:
+        return
+    times, expert_s, cores, threads, (n_tok, full_tokens) = run_reference_cpu(ws, args.workload, args.steps, args.warmup)
+    us = 1e6 * sum(times) / len(times)
+    what = "full" if n_tok == full_tokens else f"first {n_tok} of {full_tokens} tokens per rank (time scaled by {full_tokens / n_tok:.2f}) of the"
+    sample = (f"{what} {args.workload} workload at world size {ws}, {ws} gloo process(es) x {threads} torch thread(s); "
+              f"dispatch+combine wall clock between barriers, max over ranks; the expert placeholder "
+              f"(valid rows only, {1e3 * sum(expert_s) / len(expert_s):.1f} ms) is not counted")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": ws, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.workload, ws, "direct"),
+        "cpu_baseline": {"value": us, "unit": "us", "cores": min(cores, ws * threads), "kind": "port", "sample": sample},
+        "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name: str, ws: int, payload: str):
+    import gpu_mode_kernels_b200 as pkg
+
+    w = pkg.WORKLOADS[name]
+    return {
+        "workload": f"{name}: {w['num_experts']} experts ({w['num_experts'] // ws} per rank), top-{w['experts_per_token']}, "
+                    f"hidden {w['hidden_dim']}, {w['max_num_tokens']} tokens/rank, bf16, "
+                    f"{w.get('routing', 'uniform')} routing, softmax weights, seed {w['seed']}",
+        "world_size": ws, "payload": payload,
+        "global_tokens": w["max_num_tokens"] * ws,
+        "l2": "flushed between timed steps (256 MiB write, untimed)",
+    }
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def main():
+    args = parse_args()
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if ws == 1 and args.gpus > 1:
+        sys.exit("bench.py --gpus N>1 must be launched with python -m torch.distributed.run --nproc-per-node N")
+    if args.impl == "reference":
+        reference_main(args, rank, ws)
+        return
+
+    import torch.distributed as dist
+
+    import gpu_mode_kernels_b200 as pkg
+    from gpu_mode_kernels_b200 import traffic
+    from gpu_mode_kernels_b200.all2all import A2AContext
+
+    if not torch.cuda.is_available():
+        sys.exit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if ws > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
+
+    wl = pkg.WORKLOADS[args.workload]
+    payload = args.payload or wl.get("payload", "direct")
+    cfg, rd_cpu, _, _ = pkg.workload_input(args.workload, rank, ws)
+    rd = rd_cpu.to(dev)
+    T, K, H = rd.num_tokens, cfg.experts_per_token, cfg.hidden_dim
+    ctx = A2AContext(cfg, rank, ws, device=local_rank, payload=payload)
+    y = torch.empty(T, H, dtype=cfg.out_dtype, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if ws > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms_list):
+        t = torch.tensor(ms_list, dtype=torch.float64, device=dev)
+        if ws > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.cpu().tolist()
+
+    def timed_loop(step_fn, steps, warmup):
+        for i in range(warmup):
+            flush.fill_(i & 1)
+            if ws > 1:
+                ctx.barrier()
+            step_fn()
+        sync_all()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        l0 = ctx.launches
+        for i in range(steps):
+            flush.fill_(i & 1)
+            if ws > 1:
+                ctx.barrier()
+            ev[i][0].record(stream)
+            step_fn()
+            ev[i][1].record(stream)
+        sync_all()
+        launches = ctx.launches - l0
+        return max_over_ranks([a.elapsed_time(b) for a, b in ev]), launches
+
+    # ---- headline: device-resident inputs --------------------------------
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        per_step_ms, launches = timed_loop(lambda: ctx.forward(rd.x, rd.indices, rd.weights, y), args.steps, args.warmup)
+    ctx.check()
+    ms = sum(per_step_ms) / len(per_step_ms)
+
+    # ---- end to end: host buffers through the plugin-facing entry --------
+    hx, hi, hw = rd_cpu.x.pin_memory(), rd_cpu.indices.pin_memory(), rd_cpu.weights.pin_memory()
+    hy = torch.empty(T, H, dtype=cfg.out_dtype, pin_memory=True)
+    e2e_steps = min(args.steps, 200)
+    e2e_ms_list, _ = timed_loop(lambda: ctx.forward_host(hx, hi, hw, hy), e2e_steps, min(args.warmup, 10))
+    ctx.check()
+    e2e_ms = sum(e2e_ms_list) / len(e2e_ms_list)
+    h2d = hx.numel() * hx.element_size() + hi.numel() * 4 + hw.numel() * 4
+    d2h = hy.numel() * hy.element_size()
+
+    # ---- per-kernel pass: events between the four launches ---------------
+    ph_steps = min(args.steps, 200)
+    names = ["route", "dispatch_send", "recv_expert", "combine"]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(ph_steps)]
+    for i in range(ph_steps + 5):
+        flush.fill_(i & 1)
+        if ws > 1:
+            ctx.barrier()
+        e = evs[i - 5] if i >= 5 else None
+        if e: e[0].record(stream)
+        ctx.route(rd.indices)
+        if e: e[1].record(stream)
+        ctx.dispatch_send(rd.x)
+        if e: e[2].record(stream)
+        ctx.dispatch_recv_expert()
+        if e: e[3].record(stream)
+        ctx.combine(rd.weights, y)
+        if e: e[4].record(stream)
+    sync_all()
+    ctx.check()
+    phase_us = {}
+    for j, n in enumerate(names):
+        per = max_over_ranks([e[j].elapsed_time(e[j + 1]) for e in evs])
+        phase_us[n] = 1e3 * sum(per) / len(per)
+
+    # ---- traffic and roofline --------------------------------------------
+    hbm_peak, peak_kind = measured_peaks()
+    all_idx = [pkg.workload_input(args.workload, r, ws)[1].indices for r in range(ws)] if ws > 1 else [rd_cpu.indices]
+    tr = traffic.summarize(all_idx, cfg.num_experts, ws, H, payload)
+    if ws == 1:
+        alg = traffic.hbm_bytes_single_rank(T, K, H)
+        dom = max(names, key=lambda n: phase_us[n])
+        achieved = alg[dom] / (phase_us[dom] * 1e-6) / 1e9
+        roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                    "algorithmic_bytes": alg[dom], "kernel_us": phase_us[dom]}
+        nvlink = None
+    else:
+        achieved = tr["algorithmic_bytes"] / (ms * 1e-3) / 1e9
+        roofline = {"bound": "nvlink", "kernel": "dispatch_send+combine", "achieved": achieved,
+                    "peak": traffic.NVLINK_MEASURED_GBS, "unit": "GB/s", "frac": achieved / traffic.NVLINK_MEASURED_GBS,
+                    "traffic": None, "peak_kind": "of measured peer copy (770 GB/s per direction)",
+                    "algorithmic_bytes": tr["algorithmic_bytes"]}
+        nvlink = {"algorithmic_gbs": achieved, "frac_of_900": achieved / traffic.NVLINK_NOMINAL_GBS,
+                  "wire_gbs": tr["wire_bytes"] / (ms * 1e-3) / 1e9, "busiest_rows": tr["busiest_rows"],
+                  "busiest_rows_dedup": tr["busiest_rows_dedup"], "t_roof_us_900": tr["t_roof_us_nominal"]}
+
+    # ---- CPU baseline (rank 0, N=1 only): the port of the reference path --
+    cpu_baseline = None
+    if ws == 1 and not args.skip_cpu_baseline:
+        times, expert_s, cores, threads, _ = run_reference_cpu(1, args.workload, 3, 1)
+        cpu_baseline = {"value": 1e6 * min(times), "unit": "us", "cores": threads, "kind": "port",
+                        "sample": f"full {args.workload} workload at world size 1, one gloo process with {threads} torch "
+                                  f"threads; dispatch+combine of the reference's Python path, best of 3; expert "
+                                  f"placeholder on valid rows ({1e3 * min(expert_s):.1f} ms) not counted"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, ws, payload),
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "clocks": clocks.summary(),
+            "kernels_us": phase_us, "tokens_per_s": T * ws / (ms * 1e-3),
+            "p50_us": 1e3 * statistics.median(per_step_ms), "max_us": 1e3 * max(per_step_ms),
+        }
+        if nvlink is not None:
+            line["nvlink"] = nvlink
+        print(json.dumps(line), flush=True)
+
+    sync_all()
+    ctx.close()
+    if ws > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,270 @@
+"""Host side of the path: per-group context and the ``custom_kernel`` plugin entry.
+
+``A2AContext`` plays the role of ``P2PState`` in the reference's final submission
+(amd-distributed/all2all/submission_v9.py:880-947): it owns this rank's symmetric
+receive region, exchanges one handle blob per rank with a single ``all_gather``
+(NCCL or gloo -- the only collective this package ever issues) and maps the
+peers.  ``custom_kernel(data)`` has the signature the task defines
+(task.py:8-9, submission_v9.py:976-982): ``data = (cfg, rank_data, rank,
+world_size)`` in, ``[num_tokens, hidden_dim]`` tensor of ``cfg.out_dtype`` out.
+All compute is in liba2a.so; nothing here has a CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from ._lib import A2AError, Config, Status  # noqa: F401
+from .task import MoEConfig, input_t, output_t
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+class A2AContext:
+    """State of one rank for one (config, process group): buffers, peer mappings, flags."""
+
+    def __init__(self, cfg: MoEConfig, rank: int, world_size: int, *, device: Optional[int] = None,
+                 payload: str = "direct", timeout_ms: int = 2000, group=None, connect: bool = True):
+        if cfg.in_dtype != cfg.out_dtype or cfg.in_dtype not in _DTYPES:
+            raise A2AError(_lib.A2A_ERR_CONFIG, f"unsupported dtypes {cfg.in_dtype}/{cfg.out_dtype}")
+        self.lib = _lib.load()
+        self.cfg, self.rank, self.world_size = cfg, rank, world_size
+        self.payload = payload
+        if device is None:
+            device = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        self.device_index = int(device)
+        self.device = torch.device("cuda", self.device_index)
+        self.group = group
+        c = Config(rank, world_size, self.device_index, cfg.num_experts, cfg.experts_per_token,
+                   cfg.hidden_dim, cfg.max_num_tokens, _DTYPES[cfg.in_dtype], _lib.PAYLOAD[payload], timeout_ms)
+        self._h = C.c_void_p()
+        _lib.check(self.lib.a2a_create(C.byref(self._h), C.byref(c)))
+        self.num_local_experts = cfg.num_experts // world_size
+        self.max_recv = cfg.max_num_tokens * world_size
+        self._num_tokens = 0
+        if connect and world_size > 1:
+            self._connect_over_group()
+
+    # ---- bootstrap ---------------------------------------------------------
+    def export_handle(self) -> torch.Tensor:
+        n = self.lib.a2a_ipc_handle_bytes()
+        blob = torch.empty(n, dtype=torch.uint8)
+        _lib.check(self.lib.a2a_export_handle(self._h, _ptr(blob)))
+        return blob
+
+    def open_peers(self, all_blobs: torch.Tensor) -> None:
+        all_blobs = all_blobs.contiguous().cpu()
+        _lib.check(self.lib.a2a_open_peers(self._h, _ptr(all_blobs)))
+
+    def _connect_over_group(self) -> None:
+        """One all_gather of the handle blobs over the caller's process group, then map the peers."""
+        blob = self.export_handle()
+        backend = dist.get_backend(self.group)
+        on_gpu = "nccl" in str(backend)
+        mine = blob.to(self.device) if on_gpu else blob
+        gathered = torch.empty(self.world_size * blob.numel(), dtype=torch.uint8, device=mine.device)
+        dist.all_gather_into_tensor(gathered, mine, group=self.group)
+        self.open_peers(gathered)
+        # nobody may write into a region before its owner has finished zeroing it
+        # (a2a_create synchronised), and everybody has now mapped everybody
+        dist.barrier(group=self.group)
+
+    @staticmethod
+    def attach_local(ctxs: Sequence["A2AContext"]) -> None:
+        """Wire up contexts that live in this process (rank r at position r)."""
+        arr = (C.c_void_p * len(ctxs))(*[c._h for c in ctxs])
+        for c in ctxs:
+            _lib.check(c.lib.a2a_attach_local_peers(c._h, arr))
+
+    # ---- phases ------------------------------------------------------------
+    @staticmethod
+    def _stream() -> C.c_void_p:
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def route(self, indices: torch.Tensor) -> None:
+        assert indices.dtype == torch.int32 and indices.is_contiguous() and indices.is_cuda
+        self._num_tokens = indices.shape[0]
+        self._keep = [indices]
+        _lib.check(self.lib.a2a_route(self._h, _ptr(indices), self._num_tokens, self._stream()))
+
+    def dispatch_send(self, x: torch.Tensor) -> None:
+        assert x.dtype == self.cfg.in_dtype and x.is_contiguous() and x.is_cuda
+        self._keep.append(x)
+        _lib.check(self.lib.a2a_dispatch_send(self._h, _ptr(x), self._stream()))
+
+    def dispatch_recv(self) -> None:
+        _lib.check(self.lib.a2a_dispatch_recv(self._h, self._stream()))
+
+    def expert_placeholder(self) -> None:
+        _lib.check(self.lib.a2a_expert_placeholder(self._h, self._stream()))
+
+    def dispatch_recv_expert(self) -> None:
+        _lib.check(self.lib.a2a_dispatch_recv_expert(self._h, self._stream()))
+
+    def expert_done(self) -> None:
+        _lib.check(self.lib.a2a_expert_done(self._h, self._stream()))
+
+    def combine(self, weights: torch.Tensor, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        assert weights.dtype == torch.float32 and weights.is_contiguous() and weights.is_cuda
+        if y is None:
+            y = torch.empty(self._num_tokens, self.cfg.hidden_dim, dtype=self.cfg.out_dtype, device=self.device)
+        self._keep.append(weights)
+        _lib.check(self.lib.a2a_combine(self._h, _ptr(weights), _ptr(y), self._stream()))
+        return y
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """route + dispatch + expert placeholder + combine on the current stream (device tensors)."""
+        n = x.shape[0]
+        if y is None:
+            y = torch.empty(n, self.cfg.hidden_dim, dtype=self.cfg.out_dtype, device=self.device)
+        self._num_tokens = n
+        _lib.check(self.lib.a2a_forward(self._h, _ptr(x), _ptr(indices), _ptr(weights), _ptr(y), n, self._stream()))
+        return y
+
+    def forward_host(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                     y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Same for HOST tensors (pinned for speed): copies in, runs, copies out, all asynchronous."""
+        n = x.shape[0]
+        if y is None:
+            y = torch.empty(n, self.cfg.hidden_dim, dtype=self.cfg.out_dtype, pin_memory=True)
+        self._num_tokens = n
+        _lib.check(self.lib.a2a_forward_host(self._h, _ptr(x), _ptr(indices), _ptr(weights), _ptr(y), n,
+                                             self._stream()))
+        return y
+
+    def barrier(self) -> None:
+        _lib.check(self.lib.a2a_barrier(self._h, self._stream()))
+
+    # ---- inspection --------------------------------------------------------
+    def export_dispatch(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """What ``PyTorchAllToAll.dispatch`` returns (reference.py:148); padding is zero here."""
+        L, R, H = self.num_local_experts, self.max_recv, self.cfg.hidden_dim
+        counts = torch.zeros(L, dtype=torch.int32, device=self.device)
+        rows = torch.zeros(L, R, H, dtype=self.cfg.in_dtype, device=self.device)
+        meta = torch.zeros(L, R, 5, dtype=torch.int32, device=self.device)
+        _lib.check(self.lib.a2a_export_dispatch(self._h, _ptr(counts), _ptr(rows), _ptr(meta), self._stream()))
+        return counts, rows, meta
+
+    def route_tables(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Copies of the slot table [num_tokens, K] and per-expert send counts [E] of the last route."""
+        n, K, E = self._num_tokens, self.cfg.experts_per_token, self.cfg.num_experts
+        out_s = torch.empty(n, K, dtype=torch.int32, device=self.device)
+        out_c = torch.empty(E, dtype=torch.int32, device=self.device)
+        _lib.check(self.lib.a2a_copy_route(self._h, _ptr(out_s), _ptr(out_c), self._stream()))
+        return out_s, out_c
+
+    def status(self) -> Status:
+        s = Status()
+        _lib.check(self.lib.a2a_status(self._h, C.byref(s)))
+        return s
+
+    def check(self) -> None:
+        """Raise if a kernel of this context has recorded an error."""
+        s = self.status()
+        if s.code != 0:
+            raise A2AError(s.code, f"{_lib.strerror(s.code)} (rank {s.rank}, peer {s.peer}, phase {s.phase}, "
+                                   f"call {s.epoch}, detail {s.detail})")
+
+    def clear_status(self) -> None:
+        _lib.check(self.lib.a2a_status_clear(self._h))
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.a2a_launch_count(self._h))
+
+    @property
+    def symmetric_bytes(self) -> int:
+        return int(self.lib.a2a_symmetric_bytes(self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) is not None and self._h.value:
+            self.lib.a2a_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------------------
+# plugin entry point
+# ---------------------------------------------------------------------------
+_CONTEXTS: Dict[tuple, A2AContext] = {}
+DEFAULT_PAYLOAD = "direct"
+
+
+def _context_for(cfg: MoEConfig, rank: int, world_size: int, device_index: int, payload: str) -> A2AContext:
+    key = (cfg.num_experts, cfg.experts_per_token, cfg.hidden_dim, cfg.max_num_tokens, cfg.in_dtype,
+           rank, world_size, device_index, payload)
+    ctx = _CONTEXTS.get(key)
+    if ctx is None:
+        # first call with this shape: collective set-up (every rank gets here in the same call)
+        ctx = A2AContext(cfg, rank, world_size, device=device_index, payload=payload)
+        _CONTEXTS[key] = ctx
+    return ctx
+
+
+def custom_kernel(data: input_t, payload: Optional[str] = None) -> output_t:
+    """dispatch -> expert placeholder -> combine for this rank (task.py:8-9).
+
+    Device tensors in ``rank_data`` run on the current CUDA stream and return a
+    device tensor without synchronising.  Host tensors take the host entry point
+    (copies inside) and return a pinned host tensor after a stream synchronise.
+    The inputs are not modified.
+    """
+    cfg, rank_data, rank, world_size = data
+    x, idx, w = rank_data.x, rank_data.indices, rank_data.weights
+    payload = payload or DEFAULT_PAYLOAD
+    if x.is_cuda:
+        ctx = _context_for(cfg, rank, world_size, x.device.index, payload)
+        return ctx.forward(x.contiguous(), idx.contiguous(), w.contiguous())
+    ctx = _context_for(cfg, rank, world_size, torch.cuda.current_device(), payload)
+    y = ctx.forward_host(x.contiguous(), idx.contiguous(), w.contiguous())
+    torch.cuda.current_stream().synchronize()
+    return y
+
+
+def release_contexts(barrier: bool = True) -> None:
+    """Tear down every cached context (peers must have stopped touching our memory first)."""
+    if not _CONTEXTS:
+        return
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if barrier and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+    for ctx in list(_CONTEXTS.values()):
+        ctx.close()
+    _CONTEXTS.clear()
+
+
+# The task harness creates and destroys the process group per test case
+# (my_eval.py:64-85), possibly on another GPU each time, so peer mappings must
+# die with the group.  Like the reference (submission_v9.py:952-973) we hook
+# destroy_process_group; set-up needs no hook because it is lazy.
+_original_destroy = dist.destroy_process_group
+
+
+def _destroy_with_release(*args, **kwargs):
+    try:
+        release_contexts(barrier=True)
+    finally:
+        return _original_destroy(*args, **kwargs)
+
+
+def install_process_group_hooks() -> None:
+    if dist.destroy_process_group is not _destroy_with_release:
+        dist.destroy_process_group = _destroy_with_release
+
+
+install_process_group_hooks()

@@ -1,0 +1,470 @@
+// liba2a.so -- host side of the C ABI declared in include/a2a.h: context life cycle,
+// symmetric-region layout, CUDA-IPC peer mapping and kernel launches.  No torch
+// types, no allocation and no host synchronisation on the data path.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <new>
+
+#include "a2a.h"
+#include "a2a_kernels.cuh"
+
+using namespace a2a;
+
+namespace {
+
+constexpr int kNumSMs = 148;  // B200
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Layout {
+    size_t off_rows, off_meta, off_counts, off_flags, off_stage, off_stage_meta, total;
+    int stage_row_bytes;
+};
+
+Layout make_layout(const a2a_config& c) {
+    Layout l{};
+    const size_t L = c.num_experts / c.world_size, ws = c.world_size, T = c.max_num_tokens, H = c.hidden_dim;
+    size_t off = 0;
+    l.off_rows = off;
+    off = align_up(off + L * ws * T * H * 2, 256);
+    l.off_meta = off;
+    off = align_up(off + L * ws * T * sizeof(int32_t), 256);
+    l.off_counts = off;
+    off = align_up(off + ws * L * sizeof(int32_t), 256);
+    l.off_flags = off;
+    off = align_up(off + (size_t)kNumFlagKinds * A2A_MAX_WORLD * kFlagStride * sizeof(uint32_t), 256);
+    l.stage_row_bytes = 0;
+    l.off_stage = l.off_stage_meta = off;
+    l.total = off;
+    return l;
+}
+
+}  // namespace
+
+struct a2a_ctx {
+    a2a_config cfg;
+    Layout lay;
+    DevParams p;            // template of the kernel parameter block (per-call fields patched at launch)
+    uint8_t* region;        // our symmetric region (cudaMalloc)
+    uint8_t* scratch;       // local scratch (cudaMalloc)
+    size_t scratch_bytes;
+    void* ipc_mapped[A2A_MAX_WORLD];  // peers opened through CUDA IPC (to close on destroy)
+    bool peers_ready;
+    bool routed, sent;
+    uint32_t epoch, barrier_epoch;
+    int cur_tokens;
+    int64_t launches;
+    cudaStream_t side;      // private stream for status reads
+    // device staging for the host-buffer entry point
+    void* h_x;
+    int32_t* h_idx;
+    float* h_w;
+    void* h_y;
+    int route_smem;
+};
+
+namespace {
+
+#define CUDA_TRY(expr)                                   \
+    do {                                                 \
+        cudaError_t e_ = (expr);                         \
+        if (e_ != cudaSuccess) return -(int)e_;          \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool changed = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
+            changed = (cudaSetDevice(dev) == cudaSuccess);
+        }
+    }
+    ~DeviceGuard() {
+        if (changed) cudaSetDevice(prev);
+    }
+};
+
+int validate(const a2a_config& c) {
+    if (c.world_size < 1 || c.world_size > A2A_MAX_WORLD) return A2A_ERR_CONFIG;
+    if (c.rank < 0 || c.rank >= c.world_size) return A2A_ERR_CONFIG;
+    if (c.num_experts < 1 || c.num_experts > A2A_MAX_EXPERTS || c.num_experts % c.world_size != 0) return A2A_ERR_CONFIG;
+    if (c.experts_per_token < 1 || c.experts_per_token > A2A_MAX_TOPK || c.experts_per_token > c.num_experts)
+        return A2A_ERR_CONFIG;
+    if (c.hidden_dim < 8 || c.hidden_dim % 8 != 0) return A2A_ERR_CONFIG;
+    if (c.max_num_tokens < 1 || c.max_num_tokens >= (1 << 22)) return A2A_ERR_CONFIG;
+    if (c.dtype != A2A_DTYPE_BF16 && c.dtype != A2A_DTYPE_FP16) return A2A_ERR_CONFIG;
+    if (c.payload != A2A_PAYLOAD_DIRECT) return A2A_ERR_CONFIG;
+    if (c.device < 0) return A2A_ERR_CONFIG;
+    return A2A_OK;
+}
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline int grid_for(int items, int per_sm) {
+    int cap = kNumSMs * per_sm;
+    int g = items < cap ? items : cap;
+    return g < 1 ? 1 : g;
+}
+
+template <typename T, bool WAIT, bool SCALE, bool PUBLISH>
+int launch_expert_rows(a2a_ctx* c, const DevParams& p, int grid, cudaStream_t st) {
+    expert_rows_kernel<T, WAIT, SCALE, PUBLISH><<<grid, kRowThreads, 0, st>>>(p);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    return A2A_OK;
+}
+
+template <bool WAIT, bool SCALE, bool PUBLISH>
+int launch_expert_rows_dtype(a2a_ctx* c, const DevParams& p, int grid, cudaStream_t st) {
+    if (c->cfg.dtype == A2A_DTYPE_BF16) return launch_expert_rows<__nv_bfloat16, WAIT, SCALE, PUBLISH>(c, p, grid, st);
+    return launch_expert_rows<__half, WAIT, SCALE, PUBLISH>(c, p, grid, st);
+}
+
+DevParams call_params(a2a_ctx* c) {
+    DevParams p = c->p;
+    p.T = c->cur_tokens;
+    p.epoch = c->epoch;
+    return p;
+}
+
+int do_route(a2a_ctx* c, const int32_t* idx, int T, cudaStream_t st) {
+    if (!c->peers_ready) return A2A_ERR_STATE;
+    if (T < 0 || T > c->cfg.max_num_tokens || (T > 0 && idx == nullptr)) return A2A_ERR_CONFIG;
+    c->epoch++;
+    c->cur_tokens = T;
+    c->p.idx = idx;
+    DevParams p = call_params(c);
+    route_kernel<<<1, kRouteThreads, c->route_smem, st>>>(p);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    c->routed = true;
+    c->sent = false;
+    return A2A_OK;
+}
+
+int do_send(a2a_ctx* c, const void* x, cudaStream_t st) {
+    if (!c->routed || c->sent) return A2A_ERR_STATE;
+    if (c->cur_tokens > 0 && x == nullptr) return A2A_ERR_CONFIG;
+    c->p.x = x;
+    DevParams p = call_params(c);
+    const int pairs = c->cur_tokens * c->cfg.experts_per_token;
+    dispatch_send_direct_kernel<<<grid_for(pairs, 8), kRowThreads, 0, st>>>(p);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    c->sent = true;
+    return A2A_OK;
+}
+
+int do_combine(a2a_ctx* c, const float* w, void* y, cudaStream_t st) {
+    if (!c->sent) return A2A_ERR_STATE;
+    if (c->cur_tokens > 0 && (w == nullptr || y == nullptr)) return A2A_ERR_CONFIG;
+    c->p.w = w;
+    c->p.y = y;
+    DevParams p = call_params(c);
+    const int nchunk = (c->cfg.hidden_dim + kCombineChunk - 1) / kCombineChunk;
+    const int grid = grid_for(c->cur_tokens * nchunk, 16);
+    if (c->cfg.dtype == A2A_DTYPE_BF16)
+        combine_kernel<__nv_bfloat16><<<grid, kCombineThreads, 0, st>>>(p);
+    else
+        combine_kernel<__half><<<grid, kCombineThreads, 0, st>>>(p);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    return A2A_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* a2a_strerror(int status) {
+    switch (status) {
+        case A2A_OK: return "ok";
+        case A2A_ERR_CONFIG: return "invalid configuration or argument";
+        case A2A_ERR_CAPACITY: return "slab capacity exceeded (an expert got more than max_num_tokens rows from one source)";
+        case A2A_ERR_TIMEOUT: return "a device-side wait on a peer ran out of its time budget";
+        case A2A_ERR_STATE: return "call order violated";
+        case A2A_ERR_ROUTING: return "expert index out of range";
+        default: break;
+    }
+    if (status < 0) return cudaGetErrorString((cudaError_t)(-status));
+    return "unknown status";
+}
+
+size_t a2a_ipc_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
+    if (out == nullptr || cfg == nullptr) return A2A_ERR_CONFIG;
+    *out = nullptr;
+    int v = validate(*cfg);
+    if (v != A2A_OK) return v;
+    int ndev = 0;
+    CUDA_TRY(cudaGetDeviceCount(&ndev));
+    if (cfg->device >= ndev) return A2A_ERR_CONFIG;
+    DeviceGuard guard(cfg->device);
+
+    a2a_ctx* c = new (std::nothrow) a2a_ctx();
+    if (c == nullptr) return -(int)cudaErrorMemoryAllocation;
+    memset(c, 0, sizeof(*c));
+    c->cfg = *cfg;
+    if (c->cfg.timeout_ms <= 0) c->cfg.timeout_ms = 2000;
+    c->lay = make_layout(c->cfg);
+    const int E = cfg->num_experts, K = cfg->experts_per_token, T = cfg->max_num_tokens, H = cfg->hidden_dim;
+    const int L = E / cfg->world_size;
+
+    cudaError_t e = cudaMalloc(&c->region, c->lay.total);
+    if (e != cudaSuccess) { delete c; return -(int)e; }
+    // flags, counts and metadata start at zero = "epoch 0, nothing received"
+    cudaMemset(c->region + c->lay.off_meta, 0, c->lay.total - c->lay.off_meta);
+
+    // local scratch: slot | send_counts | expert_count | tickets | status | host-path staging
+    size_t off = 0;
+    const size_t o_slot = off;      off = align_up(off + (size_t)T * K * 4, 256);
+    const size_t o_send = off;      off = align_up(off + (size_t)E * 4, 256);
+    const size_t o_ecnt = off;      off = align_up(off + (size_t)L * 4, 256);
+    const size_t o_tick = off;      off = align_up(off + 8 * 4, 256);
+    const size_t o_stat = off;      off = align_up(off + sizeof(a2a_status_t), 256);
+    const size_t o_hx = off;        off = align_up(off + (size_t)T * H * 2, 256);
+    const size_t o_hy = off;        off = align_up(off + (size_t)T * H * 2, 256);
+    const size_t o_hidx = off;      off = align_up(off + (size_t)T * K * 4, 256);
+    const size_t o_hw = off;        off = align_up(off + (size_t)T * K * 4, 256);
+    c->scratch_bytes = off;
+    e = cudaMalloc(&c->scratch, off);
+    if (e != cudaSuccess) { cudaFree(c->region); delete c; return -(int)e; }
+    cudaMemset(c->scratch, 0, off);
+    e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { cudaFree(c->scratch); cudaFree(c->region); delete c; return -(int)e; }
+
+    DevParams& p = c->p;
+    p.peer[cfg->rank] = c->region;
+    p.off_rows = c->lay.off_rows; p.off_meta = c->lay.off_meta; p.off_counts = c->lay.off_counts;
+    p.off_flags = c->lay.off_flags; p.off_stage = c->lay.off_stage; p.off_stage_meta = c->lay.off_stage_meta;
+    p.stage_row_bytes = c->lay.stage_row_bytes;
+    p.rank = cfg->rank; p.ws = cfg->world_size; p.E = E; p.K = K; p.H = H; p.T_max = T; p.L = L;
+    p.timeout_ns = (long long)c->cfg.timeout_ms * 1000000LL;
+    p.slot = reinterpret_cast<int*>(c->scratch + o_slot);
+    p.send_counts = reinterpret_cast<int*>(c->scratch + o_send);
+    p.expert_count = reinterpret_cast<int*>(c->scratch + o_ecnt);
+    p.tickets = reinterpret_cast<uint32_t*>(c->scratch + o_tick);
+    p.status = reinterpret_cast<a2a_status_t*>(c->scratch + o_stat);
+    c->h_x = c->scratch + o_hx; c->h_y = c->scratch + o_hy;
+    c->h_idx = reinterpret_cast<int32_t*>(c->scratch + o_hidx);
+    c->h_w = reinterpret_cast<float*>(c->scratch + o_hw);
+
+    c->route_smem = 33 * E * (int)sizeof(int);
+    e = cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, c->route_smem);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();  // memsets done before any peer may write here
+    if (e != cudaSuccess) { a2a_destroy(c); return -(int)e; }
+    c->peers_ready = (cfg->world_size == 1);
+    *out = c;
+    return A2A_OK;
+}
+
+int a2a_destroy(a2a_ctx* c) {
+    if (c == nullptr) return A2A_OK;
+    DeviceGuard guard(c->cfg.device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < A2A_MAX_WORLD; ++r)
+        if (c->ipc_mapped[r]) cudaIpcCloseMemHandle(c->ipc_mapped[r]);
+    if (c->side) cudaStreamDestroy(c->side);
+    if (c->scratch) cudaFree(c->scratch);
+    if (c->region) cudaFree(c->region);
+    delete c;
+    return A2A_OK;
+}
+
+int a2a_export_handle(a2a_ctx* c, uint8_t* out) {
+    if (c == nullptr || out == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, c->region));
+    memcpy(out, &h, sizeof(h));
+    return A2A_OK;
+}
+
+int a2a_open_peers(a2a_ctx* c, const uint8_t* all) {
+    if (c == nullptr || all == nullptr) return A2A_ERR_CONFIG;
+    if (c->peers_ready && c->cfg.world_size > 1) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    for (int r = 0; r < c->cfg.world_size; ++r) {
+        if (r == c->cfg.rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, all + (size_t)r * sizeof(h), sizeof(h));
+        void* ptr = nullptr;
+        CUDA_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        c->ipc_mapped[r] = ptr;
+        c->p.peer[r] = static_cast<uint8_t*>(ptr);
+    }
+    c->peers_ready = true;
+    return A2A_OK;
+}
+
+int a2a_attach_local_peers(a2a_ctx* c, a2a_ctx* const* peers) {
+    if (c == nullptr || peers == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    for (int r = 0; r < c->cfg.world_size; ++r) {
+        a2a_ctx* q = peers[r];
+        if (q == nullptr || q->cfg.rank != r || q->cfg.world_size != c->cfg.world_size ||
+            q->lay.total != c->lay.total)
+            return A2A_ERR_CONFIG;
+        if (q->cfg.device != c->cfg.device) {
+            cudaError_t e = cudaDeviceEnablePeerAccess(q->cfg.device, 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (e != cudaSuccess) return -(int)e;
+        }
+        c->p.peer[r] = q->region;
+    }
+    c->peers_ready = true;
+    return A2A_OK;
+}
+
+int a2a_route(a2a_ctx* c, const int32_t* idx, int T, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    return do_route(c, idx, T, as_stream(stream));
+}
+
+int a2a_dispatch_send(a2a_ctx* c, const void* x, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    return do_send(c, x, as_stream(stream));
+}
+
+int a2a_dispatch_recv(a2a_ctx* c, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->sent) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    return launch_expert_rows_dtype<true, false, false>(c, call_params(c), 1, as_stream(stream));
+}
+
+int a2a_expert_placeholder(a2a_ctx* c, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->sent) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    return launch_expert_rows_dtype<false, true, true>(c, call_params(c), kNumSMs * 4, as_stream(stream));
+}
+
+int a2a_dispatch_recv_expert(a2a_ctx* c, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->sent) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    return launch_expert_rows_dtype<true, true, true>(c, call_params(c), kNumSMs * 4, as_stream(stream));
+}
+
+int a2a_expert_done(a2a_ctx* c, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->sent) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    return launch_expert_rows_dtype<false, false, true>(c, call_params(c), 1, as_stream(stream));
+}
+
+int a2a_combine(a2a_ctx* c, const float* w, void* y, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    return do_combine(c, w, y, as_stream(stream));
+}
+
+int a2a_forward(a2a_ctx* c, const void* x, const int32_t* idx, const float* w, void* y, int T, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    cudaStream_t st = as_stream(stream);
+    int r = do_route(c, idx, T, st);
+    if (r != A2A_OK) return r;
+    r = do_send(c, x, st);
+    if (r != A2A_OK) return r;
+    r = launch_expert_rows_dtype<true, true, true>(c, call_params(c), kNumSMs * 4, st);
+    if (r != A2A_OK) return r;
+    return do_combine(c, w, y, st);
+}
+
+int a2a_forward_host(a2a_ctx* c, const void* x, const int32_t* idx, const float* w, void* y, int T, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (T < 0 || T > c->cfg.max_num_tokens) return A2A_ERR_CONFIG;
+    if (T > 0 && (x == nullptr || idx == nullptr || w == nullptr || y == nullptr)) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    cudaStream_t st = as_stream(stream);
+    const size_t row = (size_t)c->cfg.hidden_dim * 2, tk = (size_t)T * c->cfg.experts_per_token * 4;
+    if (T > 0) {
+        CUDA_TRY(cudaMemcpyAsync(c->h_idx, idx, tk, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(c->h_x, x, row * T, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(c->h_w, w, tk, cudaMemcpyHostToDevice, st));
+    }
+    int r = a2a_forward(c, c->h_x, c->h_idx, c->h_w, c->h_y, T, stream);
+    if (r != A2A_OK) return r;
+    if (T > 0) CUDA_TRY(cudaMemcpyAsync(y, c->h_y, row * T, cudaMemcpyDeviceToHost, st));
+    return A2A_OK;
+}
+
+int a2a_barrier(a2a_ctx* c, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->peers_ready) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    c->barrier_epoch++;
+    barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(call_params(c), c->barrier_epoch);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    return A2A_OK;
+}
+
+int a2a_export_dispatch(a2a_ctx* c, int32_t* counts, void* rows, int32_t* meta, void* stream) {
+    if (c == nullptr || counts == nullptr || rows == nullptr || meta == nullptr) return A2A_ERR_CONFIG;
+    if (!c->sent) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    export_dispatch_kernel<<<kNumSMs * 2, kRowThreads, 0, as_stream(stream)>>>(call_params(c), counts,
+                                                                            static_cast<uint4*>(rows), meta);
+    c->launches++;
+    CUDA_TRY(cudaGetLastError());
+    return A2A_OK;
+}
+
+int a2a_expert_buffers(a2a_ctx* c, void** rows, int32_t** counts) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (rows) *rows = c->region + c->lay.off_rows;
+    if (counts) *counts = reinterpret_cast<int32_t*>(c->region + c->lay.off_counts);
+    return A2A_OK;
+}
+
+int a2a_route_buffers(a2a_ctx* c, int32_t** slots, int32_t** send_counts) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (slots) *slots = c->p.slot;
+    if (send_counts) *send_counts = c->p.send_counts;
+    return A2A_OK;
+}
+
+int a2a_copy_route(a2a_ctx* c, int32_t* slots_out, int32_t* send_counts_out, void* stream) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (!c->routed) return A2A_ERR_STATE;
+    DeviceGuard guard(c->cfg.device);
+    const size_t pairs = (size_t)c->cur_tokens * c->cfg.experts_per_token;
+    if (slots_out && pairs)
+        CUDA_TRY(cudaMemcpyAsync(slots_out, c->p.slot, pairs * 4, cudaMemcpyDeviceToDevice, as_stream(stream)));
+    if (send_counts_out)
+        CUDA_TRY(cudaMemcpyAsync(send_counts_out, c->p.send_counts, (size_t)c->cfg.num_experts * 4,
+                                 cudaMemcpyDeviceToDevice, as_stream(stream)));
+    return A2A_OK;
+}
+
+int a2a_status(a2a_ctx* c, a2a_status_t* out) {
+    if (c == nullptr || out == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(cudaMemcpyAsync(out, c->p.status, sizeof(*out), cudaMemcpyDeviceToHost, c->side));
+    CUDA_TRY(cudaStreamSynchronize(c->side));
+    return A2A_OK;
+}
+
+int a2a_status_clear(a2a_ctx* c) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemset(c->p.status, 0, sizeof(a2a_status_t)));
+    CUDA_TRY(cudaMemset(c->p.tickets, 0, 8 * sizeof(uint32_t)));
+    return A2A_OK;
+}
+
+int64_t a2a_launch_count(a2a_ctx* c) { return c ? c->launches : 0; }
+
+size_t a2a_symmetric_bytes(a2a_ctx* c) { return c ? c->lay.total : 0; }
+
+}  // extern "C"

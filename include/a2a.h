@@ -1,0 +1,202 @@
+/*
+ * a2a.h -- C ABI of liba2a.so: MoE all-to-all dispatch / expert placeholder /
+ * combine for NVIDIA B200 (sm_100a) over NVLink peer memory.
+ *
+ * One context per process and GPU ("rank").  Every rank owns one symmetric
+ * region of device memory (receive rows, row metadata, per-source counts,
+ * epoch flags); peers map it through CUDA IPC (or, inside one process, by
+ * pointer).  All data-path functions only enqueue kernels on the caller's
+ * stream and never synchronise with the host; they must be called by all ranks
+ * collectively, the same number of times, in the same order.
+ *
+ * Conventions: every function returns an int status -- 0 on success, a positive
+ * A2A_ERR_* code for errors detected by this library, or the negated
+ * cudaError_t for a CUDA runtime failure.  Device pointers are plain `void*`
+ * owned by the caller; `stream` is a cudaStream_t passed as `void*` (NULL =
+ * legacy default stream).  A context is not thread-safe.
+ *
+ * Each entry point cites the interface of the reference
+ * (gau-nernst/gpu-mode-kernels, amd-distributed/all2all) that it replaces.
+ */
+#ifndef A2A_H_
+#define A2A_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct a2a_ctx a2a_ctx;
+
+enum {
+    A2A_OK = 0,
+    A2A_ERR_CONFIG = 1,   /* invalid configuration or argument                          */
+    A2A_ERR_CAPACITY = 2, /* a (source, expert) slab would overflow max_num_tokens rows  */
+    A2A_ERR_TIMEOUT = 3,  /* a bounded device-side wait on a peer's flag ran out         */
+    A2A_ERR_STATE = 4,    /* call order violated (peers not attached, route missing...)  */
+    A2A_ERR_ROUTING = 5   /* an expert index outside [0, num_experts)                    */
+};
+
+enum { A2A_DTYPE_BF16 = 0, A2A_DTYPE_FP16 = 1 };
+
+/* How dispatch moves token rows to the expert ranks. */
+enum {
+    A2A_PAYLOAD_DIRECT = 0, /* one row per (token, k), stored straight into the expert's slab     */
+    A2A_PAYLOAD_DEDUP = 1,  /* one row per (token, destination rank); the receiver fans it out    */
+    A2A_PAYLOAD_FP8 = 2     /* as DEDUP, row quantised to e4m3 with one fp32 scale per 128 values */
+};
+
+enum { A2A_MAX_WORLD = 8, A2A_MAX_EXPERTS = 1024, A2A_MAX_TOPK = 32 };
+
+/* Problem description; the fields of the reference's MoEConfig (reference.py:10-17)
+ * plus the rank layout custom_kernel receives in its data tuple (reference.py:253). */
+typedef struct a2a_config {
+    int32_t rank;            /* this process' rank, 0 <= rank < world_size                   */
+    int32_t world_size;      /* 1..A2A_MAX_WORLD; num_experts % world_size == 0              */
+    int32_t device;          /* CUDA device ordinal of this rank                             */
+    int32_t num_experts;     /* E <= A2A_MAX_EXPERTS; expert e lives on rank e / (E/world)   */
+    int32_t experts_per_token; /* K <= A2A_MAX_TOPK, distinct experts per token              */
+    int32_t hidden_dim;      /* H, multiple of 8 (of 128 for A2A_PAYLOAD_FP8)                */
+    int32_t max_num_tokens;  /* upper bound of tokens per rank and call                      */
+    int32_t dtype;           /* A2A_DTYPE_*: element type of x and of the output             */
+    int32_t payload;         /* A2A_PAYLOAD_*                                                */
+    int32_t timeout_ms;      /* budget of every device-side wait; <= 0 selects 2000 ms       */
+} a2a_config;
+
+/* First error recorded by a kernel since the last a2a_status_clear(). */
+typedef struct a2a_status_t {
+    int32_t code;    /* A2A_OK or A2A_ERR_*                         */
+    int32_t rank;    /* rank that recorded it                       */
+    int32_t peer;    /* peer rank waited for, or -1                 */
+    int32_t phase;   /* 1 route, 2 dispatch-send, 3 dispatch-recv, 4 expert, 5 combine, 6 barrier */
+    uint32_t epoch;  /* call number the kernel belonged to          */
+    int32_t detail;  /* offending expert index / count / token      */
+} a2a_status_t;
+
+const char* a2a_strerror(int status);
+
+/* Validate `cfg`, select the device, allocate the symmetric region and the
+ * local scratch once (nothing is allocated or zeroed on the data path).
+ * Replaces P2PState.__init__ + p2p_state_init (submission_v9.py:881-911, :109-131). */
+int a2a_create(a2a_ctx** out, const a2a_config* cfg);
+
+/* Wait for this rank's device work, unmap peers, free everything.  The caller
+ * must make sure (host barrier) that no peer still reads this rank's memory.
+ * Replaces P2PState.close + p2p_state_destroy (submission_v9.py:913-919, :133-145). */
+int a2a_destroy(a2a_ctx* ctx);
+
+/* Size of one exported handle blob.  Replaces the fixed 64 in get_ipc_handle
+ * (submission_v9.py:61-66). */
+size_t a2a_ipc_handle_bytes(void);
+
+/* Write this rank's handle blob (a2a_ipc_handle_bytes() bytes) to `out` (host
+ * memory).  The caller all-gathers the blobs with whatever transport it has
+ * (one NCCL or gloo all_gather).  Replaces get_ipc_handle (submission_v9.py:61-66). */
+int a2a_export_handle(a2a_ctx* ctx, uint8_t* out);
+
+/* Map every peer's region from the gathered blobs (`world_size` blobs, rank
+ * order).  Replaces open_ipc_handle per peer + heap_bases (submission_v9.py:68-75, :898-899). */
+int a2a_open_peers(a2a_ctx* ctx, const uint8_t* all_handles);
+
+/* Same-process alternative to the two calls above: `peers[r]` is rank r's
+ * context living in this process (on this or another GPU).  No counterpart in
+ * the reference (it is always one process per GPU); used to run several ranks on
+ * one GPU phase by phase, and by single-process multi-GPU callers. */
+int a2a_attach_local_peers(a2a_ctx* ctx, a2a_ctx* const* peers);
+
+/* Routing: for every (token, k) the slot of its row inside the
+ * (expert, this source) slab, and per-expert send counts.  `topk_idx` is
+ * [num_tokens, K] int32 on the device.  Replaces the Python loop of
+ * PyTorchAllToAll.dispatch (reference.py:72-88) / block 0 of the v9 send kernel
+ * (submission_v9.py:272-312). */
+int a2a_route(a2a_ctx* ctx, const int32_t* topk_idx, int num_tokens, void* stream);
+
+/* Dispatch, sending half: push this rank's rows (x is [num_tokens, H], device)
+ * into the expert ranks' slabs, then publish counts and a release flag to every
+ * peer.  Never waits.  Needs a2a_route of the same call first.  Replaces the
+ * exchange of PyTorchAllToAll.dispatch (reference.py:90-120) / dispatch_kernel
+ * with DO_SEND (submission_v9.py:313-357). */
+int a2a_dispatch_send(a2a_ctx* ctx, const void* x, void* stream);
+
+/* Dispatch, receiving half: wait (bounded) until every source's rows of this
+ * call have landed; afterwards the slabs and counts are valid (for
+ * DEDUP/FP8 payloads this is also where rows are fanned out / dequantised).
+ * Replaces the regroup loop (reference.py:123-148) / dispatch_kernel with
+ * DO_RECV (submission_v9.py:365-424). */
+int a2a_dispatch_recv(a2a_ctx* ctx, void* stream);
+
+/* The reference's placeholder expert op on the valid received rows, in place:
+ * row = dtype(float(row) * (1 + rank)); then tell every home rank its outputs
+ * are ready.  Replaces reference.py:262 / fake_moe_kernel (submission_v6.py:381-446). */
+int a2a_expert_placeholder(a2a_ctx* ctx, void* stream);
+
+/* a2a_dispatch_recv and a2a_expert_placeholder fused into one kernel (wait, scale
+ * the rows as they are found valid, publish); the launch a2a_forward makes.
+ * Replaces the same reference lines as those two. */
+int a2a_dispatch_recv_expert(a2a_ctx* ctx, void* stream);
+
+/* Variant for a real expert op: the caller has overwritten the rows in place
+ * with its own kernel on `stream`; only publish readiness to the home ranks. */
+int a2a_expert_done(a2a_ctx* ctx, void* stream);
+
+/* Combine: wait (bounded) for the expert ranks, pull the K expert outputs of
+ * each token from the peers and write y[t] = dtype(sum_k float(row_k) * w[t,k])
+ * (fp32 accumulation, k ascending).  `topk_weights` is [num_tokens, K] fp32,
+ * `y` is [num_tokens, H], both on the device.  Replaces PyTorchAllToAll.combine
+ * (reference.py:151-234) / combine_kernel (submission_v9.py:480-673). */
+int a2a_combine(a2a_ctx* ctx, const float* topk_weights, void* y, void* stream);
+
+/* route + dispatch + expert placeholder + combine in one call; what
+ * custom_kernel(data) runs.  Replaces torch.ops.p2p_module.custom_kernel
+ * (submission_v9.py:734-831). */
+int a2a_forward(a2a_ctx* ctx, const void* x, const int32_t* topk_idx, const float* topk_weights,
+                void* y, int num_tokens, void* stream);
+
+/* a2a_forward for HOST buffers (pinned for speed): copies x, topk_idx and
+ * topk_weights to the device, runs the path, copies y back; all asynchronous
+ * on `stream`.  This is the call a host-resident caller of custom_kernel makes. */
+int a2a_forward_host(a2a_ctx* ctx, const void* x_host, const int32_t* topk_idx_host,
+                     const float* topk_weights_host, void* y_host, int num_tokens, void* stream);
+
+/* Cross-GPU rendezvous on the device: returns (on the stream) once every rank's
+ * stream has reached it.  Bounded wait.  Used to align ranks before timing.
+ * Plays the role of dist.barrier() around the timed call (my_eval.py:160-172). */
+int a2a_barrier(a2a_ctx* ctx, void* stream);
+
+/* Test/inspection helper: copy what PyTorchAllToAll.dispatch returns
+ * (reference.py:148) into caller-provided device buffers:
+ * counts [L] int32, rows [L, max_num_tokens*world, H], meta [L, max_num_tokens*world, 5]
+ * int32 (global_expert, src_rank, src_token, src_k, 0); rows of one expert ordered by
+ * (src_rank, token, k) like the reference.  Padding is left untouched. */
+int a2a_export_dispatch(a2a_ctx* ctx, int32_t* counts, void* rows, int32_t* meta, void* stream);
+
+/* Device pointers into this rank's own state (valid until a2a_destroy):
+ * the slab rows [L][world][max_num_tokens][H] and counts [world][L]; the layout
+ * contract a real expert kernel would consume. */
+int a2a_expert_buffers(a2a_ctx* ctx, void** rows, int32_t** counts_by_source);
+
+/* Per-(token,k) slot table [num_tokens*K] int32 and per-expert send counts
+ * [num_experts] int32 computed by the last a2a_route (device pointers). */
+int a2a_route_buffers(a2a_ctx* ctx, int32_t** slots, int32_t** send_counts);
+
+/* Test/inspection helper: copy those two tables into caller device buffers
+ * ([num_tokens*K] and [num_experts] int32) on `stream`. */
+int a2a_copy_route(a2a_ctx* ctx, int32_t* slots_out, int32_t* send_counts_out, void* stream);
+
+/* Read (and optionally clear) the first error recorded by a kernel.  Waits for
+ * nothing: reads what is there now. */
+int a2a_status(a2a_ctx* ctx, a2a_status_t* out);
+int a2a_status_clear(a2a_ctx* ctx);
+
+/* Number of kernels this context has launched so far. */
+int64_t a2a_launch_count(a2a_ctx* ctx);
+
+/* Bytes of the symmetric region / of the local scratch of this context. */
+size_t a2a_symmetric_bytes(a2a_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* A2A_H_ */

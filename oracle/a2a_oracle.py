@@ -340,3 +340,21 @@ def dispatch_multiset(expert_num_tokens, rows_of_expert, meta_of_expert):
                 raise AssertionError(f"duplicate row key {key}")
             out[key] = raw[j].numpy().tobytes()
     return out
+
+
+def route_tables(indices: torch.Tensor, num_experts: int):
+    """Host restatement of routing for one source rank: ``slot[t, k]`` = number of
+    earlier pairs (in ``for t: for k`` order, reference.py:79-80) with the same expert,
+    and the per-expert pair counts.  Literal loop; small inputs only."""
+    idx = indices.cpu().tolist()
+    seen = [0] * num_experts
+    slots = []
+    for experts in idx:
+        row = []
+        for e in experts:
+            row.append(seen[e])
+            seen[e] += 1
+        slots.append(row)
+    n_k = indices.shape[1] if indices.dim() == 2 else 0
+    return (torch.tensor(slots, dtype=torch.int32).reshape(len(idx), n_k),
+            torch.tensor(seen, dtype=torch.int32))
