@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--workload", default="c4")
     ap.add_argument("--payload", default=None, help="direct | dedup | fp8 (default: the workload's own)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--per-phase-launches", action="store_true",
+                    help="run the forward as one kernel per phase instead of one cooperative launch")
     return ap.parse_args()
 
 
@@ -221,7 +223,7 @@ def reference_main(args, rank: int, ws: int):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(name: str, ws: int, payload: str):
+def workload_config(name: str, ws: int, payload: str, launches: str = "one cooperative launch per forward"):
     import gpu_mode_kernels_b200 as pkg
 
     w = pkg.WORKLOADS[name]
@@ -229,7 +231,7 @@ def workload_config(name: str, ws: int, payload: str):
         "workload": f"{name}: {w['num_experts']} experts ({w['num_experts'] // ws} per rank), top-{w['experts_per_token']}, "
                     f"hidden {w['hidden_dim']}, {w['max_num_tokens']} tokens/rank, bf16, "
                     f"{w.get('routing', 'uniform')} routing, softmax weights, seed {w['seed']}",
-        "world_size": ws, "payload": payload,
+        "world_size": ws, "payload": payload, "launches": launches,
         "global_tokens": w["max_num_tokens"] * ws,
         "l2": "flushed between timed steps (256 MiB write, untimed)",
     }
@@ -268,6 +270,9 @@ def main():
     rd = rd_cpu.to(dev)
     T, K, H = rd.num_tokens, cfg.experts_per_token, cfg.hidden_dim
     ctx = A2AContext(cfg, rank, ws, device=local_rank, payload=payload)
+    if args.per_phase_launches:
+        ctx.set_fused(False)
+    fused = not args.per_phase_launches
     y = torch.empty(T, H, dtype=cfg.out_dtype, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
     stream = torch.cuda.current_stream()
@@ -350,11 +355,18 @@ def main():
     tr = traffic.summarize(all_idx, cfg.num_experts, ws, H, payload)
     if ws == 1:
         alg = traffic.hbm_bytes_single_rank(T, K, H)
-        dom = max(names, key=lambda n: phase_us[n])
-        achieved = alg[dom] / (phase_us[dom] * 1e-6) / 1e9
+        per_kernel = {n: {"us": phase_us[n], "algorithmic_bytes": alg[n],
+                          "gbs": alg[n] / (phase_us[n] * 1e-6) / 1e9} for n in names}
+        if fused:
+            # one launch does everything: rows written and read in dispatch, read in combine, y written
+            dom, dom_bytes, dom_us = "forward_kernel (route+send+expert+combine, one launch)", (3 * T * K + T) * 2 * H, ms * 1e3
+        else:
+            dom = max(names, key=lambda n: phase_us[n])
+            dom_bytes, dom_us = alg[dom], phase_us[dom]
+        achieved = dom_bytes / (dom_us * 1e-6) / 1e9
         roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                    "algorithmic_bytes": alg[dom], "kernel_us": phase_us[dom]}
+                    "algorithmic_bytes": dom_bytes, "kernel_us": dom_us, "per_phase_kernels": per_kernel}
         nvlink = None
     else:
         achieved = tr["algorithmic_bytes"] / (ms * 1e-3) / 1e9
@@ -379,7 +391,8 @@ def main():
         line = {
             "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, ws, payload),
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(args.workload, ws, payload,
+                                      "one cooperative launch per forward" if fused else "one kernel per phase"),
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks.summary(),

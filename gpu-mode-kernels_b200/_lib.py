@@ -53,6 +53,7 @@ SIGNATURES = {
     "a2a_expert_done": (_I, [_VP, _VP]),
     "a2a_combine": (_I, [_VP, _VP, _VP, _VP]),
     "a2a_forward": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _VP]),
+    "a2a_set_fused": (_I, [_VP, _I]),
     "a2a_forward_host": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _VP]),
     "a2a_barrier": (_I, [_VP, _VP]),
     "a2a_export_dispatch": (_I, [_VP, _VP, _VP, _VP, _VP]),
@@ -61,6 +62,8 @@ SIGNATURES = {
     "a2a_copy_route": (_I, [_VP, _VP, _VP, _VP]),
     "a2a_status": (_I, [_VP, C.POINTER(Status)]),
     "a2a_status_clear": (_I, [_VP]),
+    "a2a_trace_enable": (_I, [_VP, _I]),
+    "a2a_trace_read": (_I, [_VP, _VP, _I, C.POINTER(_I), C.POINTER(_I)]),
     "a2a_launch_count": (C.c_int64, [_VP]),
     "a2a_symmetric_bytes": (C.c_size_t, [_VP]),
 }

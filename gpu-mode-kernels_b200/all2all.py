@@ -141,6 +141,10 @@ class A2AContext:
                                              self._stream()))
         return y
 
+    def set_fused(self, on: bool) -> None:
+        """forward() as one cooperative launch (default) or as one kernel per phase."""
+        _lib.check(self.lib.a2a_set_fused(self._h, 1 if on else 0))
+
     def barrier(self) -> None:
         _lib.check(self.lib.a2a_barrier(self._h, self._stream()))
 
@@ -176,6 +180,20 @@ class A2AContext:
 
     def clear_status(self) -> None:
         _lib.check(self.lib.a2a_status_clear(self._h))
+
+    STAMPS = ("global_ns", "start", "routed", "sent", "send_arrived", "dispatch_seen", "expert_done",
+              "expert_arrived", "combine_done")
+
+    def trace_enable(self, on: bool = True) -> None:
+        """Turn the in-kernel trace on or off (synchronises the device)."""
+        _lib.check(self.lib.a2a_trace_enable(self._h, 1 if on else 0))
+
+    def trace_read(self) -> torch.Tensor:
+        """Stamps of the most recent traced launch: int64 [blocks, 16] (see STAMPS; cycles, slot 0 in ns)."""
+        buf = torch.zeros(2048, 16, dtype=torch.int64)
+        blocks, per = C.c_int(), C.c_int()
+        _lib.check(self.lib.a2a_trace_read(self._h, _ptr(buf), 2048, C.byref(blocks), C.byref(per)))
+        return buf[: blocks.value]
 
     @property
     def launches(self) -> int:

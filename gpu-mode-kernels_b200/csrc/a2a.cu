@@ -15,18 +15,20 @@ using namespace a2a;
 
 namespace {
 
-constexpr int kNumSMs = 148;  // B200
+constexpr int kTraceBlocks = 2048;  // blocks the in-kernel trace buffer has room for
+constexpr size_t kMaxSmemBytes = 200 * 1024;  // routing bitmap budget per block (227 KB is the sm_100 limit)
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Layout {
-    size_t off_rows, off_meta, off_counts, off_flags, off_stage, off_stage_meta, total;
+    size_t off_rows, off_meta, off_counts, off_src_tokens, off_flags, off_stage, off_stage_meta, total;
     int stage_row_bytes;
 };
 
 Layout make_layout(const a2a_config& c) {
     Layout l{};
     const size_t L = c.num_experts / c.world_size, ws = c.world_size, T = c.max_num_tokens, H = c.hidden_dim;
+    const size_t K = c.experts_per_token;
     size_t off = 0;
     l.off_rows = off;
     off = align_up(off + L * ws * T * H * 2, 256);
@@ -34,10 +36,19 @@ Layout make_layout(const a2a_config& c) {
     off = align_up(off + L * ws * T * sizeof(int32_t), 256);
     l.off_counts = off;
     off = align_up(off + ws * L * sizeof(int32_t), 256);
+    l.off_src_tokens = off;
+    off = align_up(off + ws * sizeof(int32_t), 256);
     l.off_flags = off;
     off = align_up(off + (size_t)kNumFlagKinds * A2A_MAX_WORLD * kFlagStride * sizeof(uint32_t), 256);
     l.stage_row_bytes = 0;
     l.off_stage = l.off_stage_meta = off;
+    if (c.payload != A2A_PAYLOAD_DIRECT) {
+        l.stage_row_bytes = (int)(c.payload == A2A_PAYLOAD_FP8 ? align_up(H + 4 * (H / kFp8Block), 16) : H * 2);
+        l.off_stage = off;
+        off = align_up(off + ws * T * (size_t)l.stage_row_bytes, 256);
+        l.off_stage_meta = off;
+        off = align_up(off + ws * T * K * sizeof(int32_t), 256);
+    }
     l.total = off;
     return l;
 }
@@ -63,7 +74,12 @@ struct a2a_ctx {
     int32_t* h_idx;
     float* h_w;
     void* h_y;
-    int route_smem;
+    int smem_bytes;         // dynamic shared memory of the routing-carrying kernels
+    int num_sms;
+    int forward_grid;       // co-resident grid of the one-launch kernel
+    bool fused;             // a2a_forward uses the one-launch kernel
+    long long* trace;       // device trace buffer (always allocated, used only while tracing is on)
+    int last_grid;          // grid of the most recent traced launch
 };
 
 namespace {
@@ -96,31 +112,22 @@ int validate(const a2a_config& c) {
     if (c.hidden_dim < 8 || c.hidden_dim % 8 != 0) return A2A_ERR_CONFIG;
     if (c.max_num_tokens < 1 || c.max_num_tokens >= (1 << 22)) return A2A_ERR_CONFIG;
     if (c.dtype != A2A_DTYPE_BF16 && c.dtype != A2A_DTYPE_FP16) return A2A_ERR_CONFIG;
-    if (c.payload != A2A_PAYLOAD_DIRECT) return A2A_ERR_CONFIG;
+    if (c.payload != A2A_PAYLOAD_DIRECT && c.payload != A2A_PAYLOAD_DEDUP && c.payload != A2A_PAYLOAD_FP8)
+        return A2A_ERR_CONFIG;
+    if (c.payload != A2A_PAYLOAD_DIRECT && (c.max_num_tokens > 65535 || c.num_experts / c.world_size > 32767))
+        return A2A_ERR_CONFIG;
+    if (c.payload == A2A_PAYLOAD_FP8 && c.hidden_dim % kFp8Block != 0) return A2A_ERR_CONFIG;
+    if (block_smem_ints(c.num_experts, c.max_num_tokens, c.experts_per_token) * sizeof(int) > kMaxSmemBytes) return A2A_ERR_CONFIG;
     if (c.device < 0) return A2A_ERR_CONFIG;
     return A2A_OK;
 }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
-inline int grid_for(int items, int per_sm) {
-    int cap = kNumSMs * per_sm;
-    int g = items < cap ? items : cap;
-    return g < 1 ? 1 : g;
-}
-
-template <typename T, bool WAIT, bool SCALE, bool PUBLISH>
-int launch_expert_rows(a2a_ctx* c, const DevParams& p, int grid, cudaStream_t st) {
-    expert_rows_kernel<T, WAIT, SCALE, PUBLISH><<<grid, kRowThreads, 0, st>>>(p);
-    c->launches++;
-    CUDA_TRY(cudaGetLastError());
-    return A2A_OK;
-}
-
-template <bool WAIT, bool SCALE, bool PUBLISH>
-int launch_expert_rows_dtype(a2a_ctx* c, const DevParams& p, int grid, cudaStream_t st) {
-    if (c->cfg.dtype == A2A_DTYPE_BF16) return launch_expert_rows<__nv_bfloat16, WAIT, SCALE, PUBLISH>(c, p, grid, st);
-    return launch_expert_rows<__half, WAIT, SCALE, PUBLISH>(c, p, grid, st);
+inline int grid_for(const a2a_ctx* c, long long items, int per_sm) {
+    long long cap = (long long)c->num_sms * per_sm;
+    long long g = items < cap ? items : cap;
+    return g < 1 ? 1 : (int)g;
 }
 
 DevParams call_params(a2a_ctx* c) {
@@ -130,32 +137,87 @@ DevParams call_params(a2a_ctx* c) {
     return p;
 }
 
-int do_route(a2a_ctx* c, const int32_t* idx, int T, cudaStream_t st) {
+// ---- kernel selection by (element type, payload) ---------------------------
+template <template <typename, int> class F, typename... A>
+auto select_tp(const a2a_ctx* c, A... a) {
+    const bool bf = c->cfg.dtype == A2A_DTYPE_BF16;
+    switch (c->cfg.payload) {
+        case A2A_PAYLOAD_DEDUP:
+            return bf ? F<__nv_bfloat16, A2A_PAYLOAD_DEDUP>::get(a...) : F<__half, A2A_PAYLOAD_DEDUP>::get(a...);
+        case A2A_PAYLOAD_FP8:
+            return bf ? F<__nv_bfloat16, A2A_PAYLOAD_FP8>::get(a...) : F<__half, A2A_PAYLOAD_FP8>::get(a...);
+        default:
+            return bf ? F<__nv_bfloat16, A2A_PAYLOAD_DIRECT>::get(a...) : F<__half, A2A_PAYLOAD_DIRECT>::get(a...);
+    }
+}
+
+using KernelFn = void (*)(DevParams);
+template <typename T, int P> struct SendSel { static KernelFn get() { return send_kernel<T, P>; } };
+template <typename T, int P> struct ForwardSel { static KernelFn get() { return forward_kernel<T, P>; } };
+template <typename T, int P> struct ExpertSel {
+    static KernelFn get(bool wait, bool fanout, bool scale, bool publish) {
+        if (wait && fanout && scale && publish) return expert_kernel<T, P, true, true, true, true>;
+        if (wait && fanout && !scale && !publish) return expert_kernel<T, P, true, true, false, false>;
+        if (!wait && !fanout && scale && publish) return expert_kernel<T, P, false, false, true, true>;
+        return expert_kernel<T, P, false, false, false, true>;
+    }
+};
+KernelFn combine_fn(const a2a_ctx* c) {
+    return c->cfg.dtype == A2A_DTYPE_BF16 ? (KernelFn)combine_kernel<__nv_bfloat16> : (KernelFn)combine_kernel<__half>;
+}
+
+int launch(a2a_ctx* c, KernelFn fn, int grid, int smem, cudaStream_t st, bool cooperative = false) {
+    DevParams p = call_params(c);
+    if (p.trace != nullptr && grid > kTraceBlocks) p.trace = nullptr;
+    if (p.trace != nullptr) c->last_grid = grid;
+    void* args[] = {&p};
+    cudaError_t e = cooperative
+        ? cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(kThreads), args, smem, st)
+        : cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), args, smem, st);
+    c->launches++;
+    if (e != cudaSuccess) return -(int)e;
+    return A2A_OK;
+}
+
+int begin_call(a2a_ctx* c, const int32_t* idx, int T) {
     if (!c->peers_ready) return A2A_ERR_STATE;
     if (T < 0 || T > c->cfg.max_num_tokens || (T > 0 && idx == nullptr)) return A2A_ERR_CONFIG;
     c->epoch++;
     c->cur_tokens = T;
     c->p.idx = idx;
-    DevParams p = call_params(c);
-    route_kernel<<<1, kRouteThreads, c->route_smem, st>>>(p);
-    c->launches++;
-    CUDA_TRY(cudaGetLastError());
     c->routed = true;
     c->sent = false;
     return A2A_OK;
+}
+
+int do_route(a2a_ctx* c, const int32_t* idx, int T, cudaStream_t st) {
+    int r = begin_call(c, idx, T);
+    if (r != A2A_OK) return r;
+    return launch(c, route_kernel, 1, c->smem_bytes, st);
 }
 
 int do_send(a2a_ctx* c, const void* x, cudaStream_t st) {
     if (!c->routed || c->sent) return A2A_ERR_STATE;
     if (c->cur_tokens > 0 && x == nullptr) return A2A_ERR_CONFIG;
     c->p.x = x;
-    DevParams p = call_params(c);
-    const int pairs = c->cur_tokens * c->cfg.experts_per_token;
-    dispatch_send_direct_kernel<<<grid_for(pairs, 8), kRowThreads, 0, st>>>(p);
-    c->launches++;
-    CUDA_TRY(cudaGetLastError());
-    c->sent = true;
-    return A2A_OK;
+    const long long items = (long long)c->cur_tokens *
+        (c->cfg.payload == A2A_PAYLOAD_DIRECT ? c->cfg.experts_per_token : c->cfg.world_size);
+    int r = launch(c, select_tp<SendSel>(c), grid_for(c, items, 8), c->smem_bytes, st);
+    if (r == A2A_OK) c->sent = true;
+    return r;
+}
+
+// grid of the receive-side kernels: a multiple of the world size so every source gets the same share
+int expert_grid(const a2a_ctx* c, int per_sm) {
+    const int ws = c->cfg.world_size;
+    int g = c->num_sms * per_sm;
+    g = (g / ws) * ws;
+    return g < ws ? ws : g;
+}
+
+int do_expert(a2a_ctx* c, bool wait, bool fanout, bool scale, bool publish, int grid, cudaStream_t st) {
+    if (!c->sent) return A2A_ERR_STATE;
+    return launch(c, select_tp<ExpertSel>(c, wait, fanout, scale, publish), grid, c->smem_bytes, st);
 }
 
 int do_combine(a2a_ctx* c, const float* w, void* y, cudaStream_t st) {
@@ -163,16 +225,9 @@ int do_combine(a2a_ctx* c, const float* w, void* y, cudaStream_t st) {
     if (c->cur_tokens > 0 && (w == nullptr || y == nullptr)) return A2A_ERR_CONFIG;
     c->p.w = w;
     c->p.y = y;
-    DevParams p = call_params(c);
-    const int nchunk = (c->cfg.hidden_dim + kCombineChunk - 1) / kCombineChunk;
-    const int grid = grid_for(c->cur_tokens * nchunk, 16);
-    if (c->cfg.dtype == A2A_DTYPE_BF16)
-        combine_kernel<__nv_bfloat16><<<grid, kCombineThreads, 0, st>>>(p);
-    else
-        combine_kernel<__half><<<grid, kCombineThreads, 0, st>>>(p);
-    c->launches++;
-    CUDA_TRY(cudaGetLastError());
-    return A2A_OK;
+    const int nseg = (c->cfg.hidden_dim / 8 + 31) / 32;
+    const long long warps = (long long)c->cur_tokens * nseg;
+    return launch(c, combine_fn(c), grid_for(c, (warps + kThreads / 32 - 1) / (kThreads / 32), 8), 0, st);
 }
 
 }  // namespace
@@ -219,13 +274,13 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     // flags, counts and metadata start at zero = "epoch 0, nothing received"
     cudaMemset(c->region + c->lay.off_meta, 0, c->lay.total - c->lay.off_meta);
 
-    // local scratch: slot | send_counts | expert_count | tickets | status | host-path staging
+    // local scratch: slot | send_counts | tickets | status | host-path staging
     size_t off = 0;
     const size_t o_slot = off;      off = align_up(off + (size_t)T * K * 4, 256);
     const size_t o_send = off;      off = align_up(off + (size_t)E * 4, 256);
-    const size_t o_ecnt = off;      off = align_up(off + (size_t)L * 4, 256);
     const size_t o_tick = off;      off = align_up(off + 8 * 4, 256);
     const size_t o_stat = off;      off = align_up(off + sizeof(a2a_status_t), 256);
+    const size_t o_trace = off;     off = align_up(off + (size_t)kTraceBlocks * kNumStamps * 8, 256);
     const size_t o_hx = off;        off = align_up(off + (size_t)T * H * 2, 256);
     const size_t o_hy = off;        off = align_up(off + (size_t)T * H * 2, 256);
     const size_t o_hidx = off;      off = align_up(off + (size_t)T * K * 4, 256);
@@ -240,21 +295,41 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     DevParams& p = c->p;
     p.peer[cfg->rank] = c->region;
     p.off_rows = c->lay.off_rows; p.off_meta = c->lay.off_meta; p.off_counts = c->lay.off_counts;
+    p.off_src_tokens = c->lay.off_src_tokens;
     p.off_flags = c->lay.off_flags; p.off_stage = c->lay.off_stage; p.off_stage_meta = c->lay.off_stage_meta;
     p.stage_row_bytes = c->lay.stage_row_bytes;
     p.rank = cfg->rank; p.ws = cfg->world_size; p.E = E; p.K = K; p.H = H; p.T_max = T; p.L = L;
     p.timeout_ns = (long long)c->cfg.timeout_ms * 1000000LL;
     p.slot = reinterpret_cast<int*>(c->scratch + o_slot);
     p.send_counts = reinterpret_cast<int*>(c->scratch + o_send);
-    p.expert_count = reinterpret_cast<int*>(c->scratch + o_ecnt);
     p.tickets = reinterpret_cast<uint32_t*>(c->scratch + o_tick);
     p.status = reinterpret_cast<a2a_status_t*>(c->scratch + o_stat);
+    c->trace = reinterpret_cast<long long*>(c->scratch + o_trace);
     c->h_x = c->scratch + o_hx; c->h_y = c->scratch + o_hy;
     c->h_idx = reinterpret_cast<int32_t*>(c->scratch + o_hidx);
     c->h_w = reinterpret_cast<float*>(c->scratch + o_hw);
 
-    c->route_smem = 33 * E * (int)sizeof(int);
-    e = cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, c->route_smem);
+    // Kernel attributes are per function and device, not per context: opt every routing-carrying
+    // kernel in for the whole shared-memory budget, then size this context's own launches.
+    c->smem_bytes = (int)(block_smem_ints(E, T, K) * sizeof(int));
+    KernelFn fns[] = {route_kernel, select_tp<SendSel>(c), select_tp<ForwardSel>(c),
+                      select_tp<ExpertSel>(c, true, true, true, true), select_tp<ExpertSel>(c, true, true, false, false),
+                      select_tp<ExpertSel>(c, false, false, true, true), select_tp<ExpertSel>(c, false, false, false, true)};
+    for (KernelFn fn : fns) {
+        e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmemBytes);
+        if (e != cudaSuccess) break;
+    }
+    int coop = 0, occ = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&c->num_sms, cudaDevAttrMultiProcessorCount, cfg->device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, cfg->device);
+    if (e == cudaSuccess)
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)select_tp<ForwardSel>(c), kThreads,
+                                                          c->smem_bytes);
+    if (e == cudaSuccess) {
+        if (occ > 8) occ = 8;
+        c->forward_grid = c->num_sms * occ;
+        c->fused = (coop != 0 && occ >= 1);
+    }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();  // memsets done before any peer may write here
     if (e != cudaSuccess) { a2a_destroy(c); return -(int)e; }
     c->peers_ready = (cfg->world_size == 1);
@@ -334,30 +409,28 @@ int a2a_dispatch_send(a2a_ctx* c, const void* x, void* stream) {
 
 int a2a_dispatch_recv(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
-    if (!c->sent) return A2A_ERR_STATE;
     DeviceGuard guard(c->cfg.device);
-    return launch_expert_rows_dtype<true, false, false>(c, call_params(c), 1, as_stream(stream));
+    // DIRECT: rows are already in place, one block just waits for every source.
+    const int grid = c->cfg.payload == A2A_PAYLOAD_DIRECT ? 1 : expert_grid(c, 4);
+    return do_expert(c, true, true, false, false, grid, as_stream(stream));
 }
 
 int a2a_expert_placeholder(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
-    if (!c->sent) return A2A_ERR_STATE;
     DeviceGuard guard(c->cfg.device);
-    return launch_expert_rows_dtype<false, true, true>(c, call_params(c), kNumSMs * 4, as_stream(stream));
+    return do_expert(c, false, false, true, true, expert_grid(c, 4), as_stream(stream));
 }
 
 int a2a_dispatch_recv_expert(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
-    if (!c->sent) return A2A_ERR_STATE;
     DeviceGuard guard(c->cfg.device);
-    return launch_expert_rows_dtype<true, true, true>(c, call_params(c), kNumSMs * 4, as_stream(stream));
+    return do_expert(c, true, true, true, true, expert_grid(c, 4), as_stream(stream));
 }
 
 int a2a_expert_done(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
-    if (!c->sent) return A2A_ERR_STATE;
     DeviceGuard guard(c->cfg.device);
-    return launch_expert_rows_dtype<false, false, true>(c, call_params(c), 1, as_stream(stream));
+    return do_expert(c, false, false, false, true, 1, as_stream(stream));
 }
 
 int a2a_combine(a2a_ctx* c, const float* w, void* y, void* stream) {
@@ -366,15 +439,31 @@ int a2a_combine(a2a_ctx* c, const float* w, void* y, void* stream) {
     return do_combine(c, w, y, as_stream(stream));
 }
 
+int a2a_set_fused(a2a_ctx* c, int on) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    if (on && c->forward_grid < 1) return A2A_ERR_STATE;
+    c->fused = (on != 0);
+    return A2A_OK;
+}
+
 int a2a_forward(a2a_ctx* c, const void* x, const int32_t* idx, const float* w, void* y, int T, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
     DeviceGuard guard(c->cfg.device);
     cudaStream_t st = as_stream(stream);
-    int r = do_route(c, idx, T, st);
+    int r = begin_call(c, idx, T);
     if (r != A2A_OK) return r;
+    if (T > 0 && (x == nullptr || w == nullptr || y == nullptr)) return A2A_ERR_CONFIG;
+    if (c->fused) {
+        c->p.x = x;
+        c->p.w = w;
+        c->p.y = y;
+        r = launch(c, select_tp<ForwardSel>(c), c->forward_grid, c->smem_bytes, st, /*cooperative=*/true);
+        if (r == A2A_OK) c->sent = true;
+        return r;
+    }
     r = do_send(c, x, st);
     if (r != A2A_OK) return r;
-    r = launch_expert_rows_dtype<true, true, true>(c, call_params(c), kNumSMs * 4, st);
+    r = do_expert(c, true, true, true, true, expert_grid(c, 4), st);
     if (r != A2A_OK) return r;
     return do_combine(c, w, y, st);
 }
@@ -412,8 +501,8 @@ int a2a_export_dispatch(a2a_ctx* c, int32_t* counts, void* rows, int32_t* meta, 
     if (c == nullptr || counts == nullptr || rows == nullptr || meta == nullptr) return A2A_ERR_CONFIG;
     if (!c->sent) return A2A_ERR_STATE;
     DeviceGuard guard(c->cfg.device);
-    export_dispatch_kernel<<<kNumSMs * 2, kRowThreads, 0, as_stream(stream)>>>(call_params(c), counts,
-                                                                            static_cast<uint4*>(rows), meta);
+    export_dispatch_kernel<<<c->num_sms * 2, kThreads, 0, as_stream(stream)>>>(call_params(c), counts,
+                                                                              static_cast<uint4*>(rows), meta);
     c->launches++;
     CUDA_TRY(cudaGetLastError());
     return A2A_OK;
@@ -443,6 +532,26 @@ int a2a_copy_route(a2a_ctx* c, int32_t* slots_out, int32_t* send_counts_out, voi
     if (send_counts_out)
         CUDA_TRY(cudaMemcpyAsync(send_counts_out, c->p.send_counts, (size_t)c->cfg.num_experts * 4,
                                  cudaMemcpyDeviceToDevice, as_stream(stream)));
+    return A2A_OK;
+}
+
+int a2a_trace_enable(a2a_ctx* c, int on) {
+    if (c == nullptr) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(cudaDeviceSynchronize());
+    if (on) CUDA_TRY(cudaMemset(c->trace, 0, (size_t)kTraceBlocks * kNumStamps * 8));
+    c->p.trace = on ? c->trace : nullptr;
+    return A2A_OK;
+}
+
+int a2a_trace_read(a2a_ctx* c, int64_t* out, int max_blocks, int* blocks, int* stamps_per_block) {
+    if (c == nullptr || out == nullptr || max_blocks < 0) return A2A_ERR_CONFIG;
+    DeviceGuard guard(c->cfg.device);
+    CUDA_TRY(cudaDeviceSynchronize());
+    int n = c->last_grid < max_blocks ? c->last_grid : max_blocks;
+    if (n > 0) CUDA_TRY(cudaMemcpy(out, c->trace, (size_t)n * kNumStamps * 8, cudaMemcpyDeviceToHost));
+    if (blocks) *blocks = n;
+    if (stamps_per_block) *stamps_per_block = kNumStamps;
     return A2A_OK;
 }
 

@@ -1,18 +1,22 @@
 // Device-side building blocks shared by the all-to-all kernels: parameter block,
-// system-scope flag operations with bounded waits, 16-byte row access, block scan.
+// system-scope flag operations with bounded waits, 16-byte row access, block scan,
+// element conversions (bf16 / fp16 / fp8 e4m3).
 //
 // Memory-ordering protocol used throughout (producer on GPU A, consumer on GPU B):
-//   producer threads: plain stores to B's memory -> __threadfence_system() ->
-//   block barrier -> one thread: atomic ticket on A; the block that draws the last
-//   ticket fences again and writes the flag with st.release.sys into B's memory.
+//   producer threads: plain stores to B's memory -> block barrier -> ONE thread per
+//   block: __threadfence_system() and an atomic ticket on A; the block that draws the
+//   last ticket fences again and writes the flag with st.release.sys into B's memory.
+//   (One fence per block, not per thread: with a system fence in every thread the membar
+//   stall was the largest stall reason of the sending kernel, 53 of ~130 cycles per issue.)
 //   consumer: ld.acquire.sys on its own flag until it carries this call's epoch
-//   (bounded by a wall-clock budget), block barrier, then plain loads.
+//   (bounded by a wall-clock budget), block/warp barrier, then plain loads.
 // Flags carry a monotonically increasing call number ("epoch"), are never reset,
 // and every (source, destination) pair has its own flag word on its own 128-byte line.
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -20,9 +24,18 @@
 
 namespace a2a {
 
+constexpr int kThreads = 256;    // every kernel of the path runs 256-thread blocks
 constexpr int kFlagStride = 32;  // uint32 words between two flags = 128 bytes
+constexpr int kFp8Block = 128;   // elements sharing one fp32 scale
 enum FlagKind : int { kFlagDispatch = 0, kFlagExpert = 1, kFlagBarrier = 2, kNumFlagKinds = 3 };
 enum Phase : int { kPhaseRoute = 1, kPhaseSend = 2, kPhaseRecv = 3, kPhaseExpert = 4, kPhaseCombine = 5, kPhaseBarrier = 6 };
+enum Ticket : int { kTicketSend = 0, kTicketExpert = 1 };
+// In-kernel trace: thread 0 of every block stamps these points with the SM cycle counter
+// (slot 0 additionally holds the nanosecond global timer so blocks can be aligned).
+enum Stamp : int {
+    kStampGlobalNs = 0, kStampStart, kStampRouted, kStampSent, kStampSendArrived, kStampDispatchSeen,
+    kStampExpertDone, kStampExpertArrived, kStampCombineDone, kNumStamps = 16
+};
 
 // Everything a kernel needs, passed by value (lives in the constant bank).
 struct DevParams {
@@ -31,7 +44,8 @@ struct DevParams {
     size_t off_rows;        // [L][ws][T_max][H] elements: slab (l, src) holds the rows src sent to local expert l
     size_t off_meta;        // [L][ws][T_max] int32: (token << 8) | k of every row
     size_t off_counts;      // [ws][L] int32: rows source s sent to local expert l in the current call
-    size_t off_flags;       // [kNumFlagKinds][ws][kFlagStride] uint32 epochs
+    size_t off_src_tokens;  // [ws] int32: tokens source s holds in the current call
+    size_t off_flags;       // [kNumFlagKinds][A2A_MAX_WORLD][kFlagStride] uint32 epochs
     size_t off_stage;       // [ws][T_max][stage_row_bytes]: one wire row per (source, token)   (DEDUP / FP8)
     size_t off_stage_meta;  // [ws][T_max][K] int32: (local_expert << 16 | slot) or -1 per k   (DEDUP / FP8)
     int stage_row_bytes;
@@ -42,9 +56,9 @@ struct DevParams {
     // local scratch of this rank
     int* slot;              // [T_max*K] slot of pair (t,k) inside slab (expert, this rank), -1 = dropped
     int* send_counts;       // [E]
-    int* expert_count;      // [L] rows per local expert summed over sources
-    uint32_t* tickets;      // [8] block-arrival counters, one per kernel kind
+    uint32_t* tickets;      // [8] block-arrival counters, one per phase
     a2a_status_t* status;
+    long long* trace;       // [blocks][kNumStamps] or nullptr when tracing is off
     // caller tensors of the current call
     const int* idx;
     const void* x;
@@ -56,6 +70,13 @@ __device__ __forceinline__ long long global_ns() {
     long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+
+__device__ __forceinline__ void stamp(const DevParams& p, int which) {
+    if (p.trace != nullptr && threadIdx.x == 0) {
+        p.trace[(size_t)blockIdx.x * kNumStamps + which] = clock64();
+        if (which == kStampStart) p.trace[(size_t)blockIdx.x * kNumStamps + kStampGlobalNs] = global_ns();
+    }
 }
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -77,11 +98,15 @@ __device__ __forceinline__ int ld_volatile_i32(const int* p) {
 // Read-only 16-byte load of caller input (never written while the kernel runs).
 __device__ __forceinline__ uint4 ld_input(const uint4* p) { return __ldg(p); }
 
-// 16-byte load of data another GPU (or an earlier phase) produced: skip L1, one use.
+// Loads of data another GPU, another block or an earlier phase produced: skip L1.
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcg(p); }
+__device__ __forceinline__ uint2 ld_stream(const uint2* p) { return __ldcg(p); }
+__device__ __forceinline__ int ld_stream(const int* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcg(p); }
 
-// 16-byte store that will not be re-read by this SM.
+// Stores that this SM will not read back.
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcg(p, v); }
+__device__ __forceinline__ void st_stream(uint2* p, uint2 v) { __stcg(p, v); }
 
 __device__ __forceinline__ void record_error(a2a_status_t* st, int code, int rank, int peer, int phase,
                                              uint32_t epoch, int detail) {
@@ -100,16 +125,25 @@ __device__ __forceinline__ uint32_t* flag_ptr(uint8_t* region_base, size_t off_f
 }
 
 // Spin until *flag has reached `epoch` (wrap-safe).  Gives up after timeout_ns, or as
-// soon as any thread of this rank has recorded an error, and returns false.
+// soon as any thread of this rank has recorded a timeout (so that one missing peer costs
+// one budget, not one per waiter), and returns false.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
     if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
     const long long t0 = global_ns();
     unsigned backoff = 32;
     for (;;) {
         if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-        if (ld_volatile_i32(&p.status->code) != 0) return false;
+        if (ld_volatile_i32(&p.status->code) == A2A_ERR_TIMEOUT) return false;
         if (global_ns() - t0 > p.timeout_ns) {
-            record_error(p.status, A2A_ERR_TIMEOUT, p.rank, peer, phase, epoch, 0);
+            // a timeout outranks whatever was recorded before: the other waiters key on it
+            if (atomicExch(&p.status->code, A2A_ERR_TIMEOUT) != A2A_ERR_TIMEOUT) {
+                p.status->rank = p.rank;
+                p.status->peer = peer;
+                p.status->phase = phase;
+                p.status->epoch = epoch;
+                p.status->detail = 0;
+                __threadfence();
+            }
             return false;
         }
         __nanosleep(backoff);
@@ -117,30 +151,32 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
     }
 }
 
-// All threads of the block call this after their last store of the kernel.  Returns
-// true in exactly one block of the grid: the one that arrived last, after which every
-// store of every block is ordered before whatever that block publishes next.
+// All threads of the block call this after their last store of a phase.  Returns true
+// in exactly one block of the grid: the one that arrived last, after which every store
+// of every block is ordered before whatever that block publishes next.
 __device__ __forceinline__ bool grid_arrive_last(uint32_t* ticket) {
     __shared__ int s_last;
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const uint32_t t = atomicAdd(ticket, 1u);
         const int last = (t == gridDim.x - 1);
-        if (last) *ticket = 0;  // everyone has arrived: re-arm for the next launch
-        __threadfence_system();
+        if (last) {
+            *ticket = 0;  // everyone has arrived: re-arm for the next launch
+            __threadfence_system();
+        }
         s_last = last;
     }
     __syncthreads();
     return s_last != 0;
 }
 
-// Exclusive prefix sum over n <= 4*blockDim.x ints held in shared memory `a`
-// (in place; a[n] receives the total).  blockDim.x must be 256.
+// Exclusive prefix sum over n <= 4*kThreads ints held in shared memory `a`
+// (in place; a[n] receives the total).  All kThreads threads must call it.
 __device__ __forceinline__ void block_exclusive_scan(int* a, int n) {
-    __shared__ int s_warp[8];
+    __shared__ int s_warp[kThreads / 32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int per = (n + 255) / 256;
+    const int per = (n + kThreads - 1) / kThreads;
     const int lo = tid * per;
     int sum = 0;
     __syncthreads();  // a[] was filled by other threads
@@ -163,7 +199,7 @@ __device__ __forceinline__ void block_exclusive_scan(int* a, int n) {
             a[lo + i] = run;
             run += v;
         }
-    if (tid == 255) a[n] = base + inc;
+    if (tid == kThreads - 1) a[n] = base + inc;
     __syncthreads();
 }
 
@@ -211,6 +247,41 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = Vec2<T>::from_float2(make_float2(f[2 * i], f[2 * i + 1]));
     return v;
+}
+
+// The placeholder expert op on 8 elements: dtype(float(x) * scale), one rounding.
+template <typename T>
+__device__ __forceinline__ uint4 scale8(const uint4& v, float scale) {
+    float f[8];
+    unpack8<T>(v, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= scale;
+    return pack8<T>(f);
+}
+
+// 8 floats -> 8 e4m3 bytes (round to nearest even, saturating to +-448)
+__device__ __forceinline__ uint2 pack8_e4m3(const float (&f)[8]) {
+    uint2 q;
+    unsigned short h[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        h[i] = __nv_cvt_float2_to_fp8x2(make_float2(f[2 * i], f[2 * i + 1]), __NV_SATFINITE, __NV_E4M3);
+    q.x = (unsigned)h[0] | ((unsigned)h[1] << 16);
+    q.y = (unsigned)h[2] | ((unsigned)h[3] << 16);
+    return q;
+}
+
+// 8 e4m3 bytes -> 8 floats (exact)
+__device__ __forceinline__ void unpack8_e4m3(const uint2& q, float (&f)[8]) {
+    const unsigned short h[4] = {(unsigned short)(q.x & 0xffff), (unsigned short)(q.x >> 16),
+                                 (unsigned short)(q.y & 0xffff), (unsigned short)(q.y >> 16)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(h[i], __NV_E4M3);
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&r));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
 }
 
 }  // namespace a2a

@@ -1,293 +1,503 @@
-// The hot-path kernels: routing, dispatch (send / receive), expert placeholder,
-// combine, plus the export and barrier helpers.  Hand-written for sm_100a; all of
-// them are bound by NVLink or HBM bandwidth (there is no contraction on this path),
-// so they are built from 16-byte vector accesses, grids sized in multiples of the
-// 148 SMs, and flag traffic kept off the critical path.
+// The hot path: routing, dispatch (send / receive), expert placeholder, combine --
+// as phases (device functions) that run either as separate kernels (the public
+// phase entry points) or back to back inside ONE cooperative kernel (a2a_forward).
+// Hand-written for sm_100a.  Every phase is bound by NVLink or HBM bandwidth (there
+// is no contraction on this path), so the work is 16-byte vector traffic spread over
+// a grid that is a multiple of the SM count, with flag traffic kept off the row path.
 #pragma once
 
 #include "a2a_device.cuh"
 
 namespace a2a {
 
-constexpr int kRouteThreads = 1024;
-constexpr int kRowThreads = 256;      // threads that move one row together
-constexpr int kCombineThreads = 128;  // threads per (token, chunk) item
-constexpr int kCombineChunk = kCombineThreads * 8;  // elements per combine item
-
-enum Ticket : int { kTicketSend = 0, kTicketExpert = 1 };
-
 // ---------------------------------------------------------------------------
-// K1 routing.  One block walks the (token, k) pairs in order, 1024 per step:
-// a warp match gives each pair its rank among the equal experts of its warp,
-// a per-expert exclusive scan over the 32 warp counts (plus the running total
-// of earlier steps) gives the warp's base.  slot[p] = number of earlier pairs
-// of this rank with the same expert -- the position the CPU reference gives the
-// row inside one source's contribution (reference.py:79-86, :140-146).
+// Shared-memory carve-up of a block (dynamic shared memory, ints):
+//   bits [Wc][E]  bit t%32 of word t/32 set iff token t of this rank uses expert e
+//   wpre [Wc][E]  number of set bits in the words before w (exclusive scan over w)
+//   cnt  [E]      tokens using expert e = rows this rank sends to e
+//   pre  [E+2]    scratch for the receive-side prefix sums
+//   idx  [T*K]    this rank's top-k expert indices (one coalesced pass over global memory;
+//                 every later look-up, including the repeat check, is a shared-memory read)
+// Wc = ceil(T/32) words of the current call; the allocation is sized for T_max.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kRouteThreads) route_kernel(const __grid_constant__ DevParams p) {
-    extern __shared__ int smem[];
-    int* warp_cnt = smem;             // [32][E]
-    int* running = smem + 32 * p.E;   // [E]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int E = p.E, P = p.T * p.K;
-    for (int e = tid; e < E; e += kRouteThreads) running[e] = 0;
-    for (int p0 = 0; p0 < P; p0 += kRouteThreads) {
-        for (int i = tid; i < 32 * E; i += kRouteThreads) warp_cnt[i] = 0;
-        __syncthreads();
-        const int pair = p0 + tid;
-        int e = -1;
-        if (pair < P) {
-            e = p.idx[pair];
-            if (e < 0 || e >= E) {
-                record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
-                e = -1;
-            }
-        }
-        const unsigned same = __match_any_sync(0xffffffffu, e);
-        const int before = __popc(same & ((1u << lane) - 1u));
-        if (e >= 0 && before == 0) warp_cnt[warp * E + e] = __popc(same);
-        __syncthreads();
-        for (int ee = tid; ee < E; ee += kRouteThreads) {
-            int run = running[ee];
-#pragma unroll 8
-            for (int w = 0; w < 32; ++w) {
-                const int c = warp_cnt[w * E + ee];
-                warp_cnt[w * E + ee] = run;
-                run += c;
-            }
-            running[ee] = run;
-        }
-        __syncthreads();
-        if (pair < P) {
-            int s = -1;
-            if (e >= 0) {
-                s = warp_cnt[warp * E + e] + before;
-                if (s >= p.T_max) {
-                    record_error(p.status, A2A_ERR_CAPACITY, p.rank, -1, kPhaseRoute, p.epoch, e);
-                    s = -1;
-                }
-            }
-            p.slot[pair] = s;
-        }
-        __syncthreads();
-    }
-    for (int e = tid; e < E; e += kRouteThreads) p.send_counts[e] = min(running[e], p.T_max);
+struct BlockSmem {
+    unsigned* bits;
+    int* wpre;
+    int* cnt;
+    int* pre;
+    int* idx;
+};
+
+__host__ __device__ inline size_t block_smem_ints(int E, int T_max, int K) {
+    const size_t W = (size_t)(T_max + 31) / 32;
+    return 2 * W * E + E + (size_t)E + 2 + (size_t)T_max * K;
 }
 
-// Publish this rank's per-expert counts and the dispatch flag to every peer.
-// Called by all threads of the one block that arrived last.
-__device__ __forceinline__ void publish_dispatch(const DevParams& p) {
+__device__ __forceinline__ BlockSmem carve_smem(int* base, int E, int T_max) {
+    const size_t W = (size_t)(T_max + 31) / 32;
+    BlockSmem s;
+    s.bits = reinterpret_cast<unsigned*>(base);
+    s.wpre = base + W * E;
+    s.cnt = base + 2 * W * E;
+    s.pre = s.cnt + E;
+    s.idx = s.pre + E + 2;
+    return s;
+}
+
+// ---------------------------------------------------------------------------
+// Routing.  Top-k experts of one token are distinct, so the slot of pair (t,k)
+// inside slab (expert e, this source) -- "number of earlier pairs of this rank
+// with the same expert", the order of the CPU reference (reference.py:79-86,
+// :140-146) -- equals the number of tokens t' < t that use e.  Every block builds
+// the [expert x token] bitmap of the whole rank in its own shared memory (T*K
+// atomicOr on shared memory, 8 KB of indices from L2), scans the words per expert,
+// and can then answer any slot with one popc.  A pair whose expert is out of range,
+// or repeats an expert of an earlier k of its token, is reported (A2A_ERR_ROUTING)
+// and dropped: it gets slot -1, sends nothing and contributes nothing.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ bool pair_is_valid(const DevParams& p, const BlockSmem& s, int t, int k, int e) {
+    if (e < 0 || e >= p.E) return false;
+    const int* row = s.idx + t * p.K;
+    bool repeat = false;
+    for (int kk = 0; kk < k; ++kk) repeat |= (row[kk] == e);
+    return !repeat;
+}
+
+__device__ __forceinline__ void route_build(const DevParams& p, const BlockSmem& s) {
     const int tid = threadIdx.x;
-    for (int e = tid; e < p.E; e += blockDim.x) {
-        const int d = e / p.L, l = e - d * p.L;
-        int* counts = reinterpret_cast<int*>(p.peer[d] + p.off_counts);
-        counts[p.rank * p.L + l] = p.send_counts[e];
+    const int E = p.E, K = p.K, P = p.T * p.K;
+    const int Wc = (p.T + 31) >> 5;
+    for (int pair = tid; pair < P; pair += kThreads) s.idx[pair] = __ldg(p.idx + pair);
+    for (int i = tid; i < Wc * E; i += kThreads) s.bits[i] = 0u;
+    __syncthreads();
+    for (int pair = tid; pair < P; pair += kThreads) {
+        const int e = s.idx[pair];
+        const int t = pair / K, k = pair - t * K;
+        if (!pair_is_valid(p, s, t, k, e)) {
+            record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+            continue;
+        }
+        atomicOr(&s.bits[(t >> 5) * E + e], 1u << (t & 31));
     }
-    __threadfence_system();
+    __syncthreads();
+    for (int e = tid; e < E; e += kThreads) {
+        int run = 0;
+        for (int w = 0; w < Wc; ++w) {
+            s.wpre[w * E + e] = run;
+            run += __popc(s.bits[w * E + e]);
+        }
+        s.cnt[e] = run;
+    }
+    __syncthreads();
+}
+
+// Slot of pair (t,k) with expert e, or -1 if the pair is dropped.
+__device__ __forceinline__ int pair_slot(const DevParams& p, const BlockSmem& s, int t, int k, int e) {
+    if (!pair_is_valid(p, s, t, k, e)) return -1;
+    const int w = t >> 5;
+    return s.wpre[w * p.E + e] + __popc(s.bits[w * p.E + e] & ((1u << (t & 31)) - 1u));
+}
+
+// Publish this rank's per-expert counts, its token count and the dispatch flag to
+// every peer.  Called by all threads of the one block that arrived last.
+__device__ __forceinline__ void publish_dispatch(const DevParams& p, const BlockSmem& s) {
+    const int tid = threadIdx.x;
+    for (int e = tid; e < p.E; e += kThreads) {
+        const int d = e / p.L, l = e - d * p.L;
+        reinterpret_cast<int*>(p.peer[d] + p.off_counts)[p.rank * p.L + l] = s.cnt[e];
+        p.send_counts[e] = s.cnt[e];
+    }
+    if (tid < p.ws) reinterpret_cast<int*>(p.peer[tid] + p.off_src_tokens)[p.rank] = p.T;
+    __syncthreads();
+    if (tid == 0) __threadfence_system();
     __syncthreads();
     if (tid < p.ws) st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagDispatch, p.rank), p.epoch);
 }
 
-// ---------------------------------------------------------------------------
-// K2 dispatch, sending half, DIRECT payload.  One block per (token, k) pair at a
-// time: 256 threads read the row from HBM/L2 with up to four 16-byte loads each in
-// flight and store it straight into slab (expert, this rank) of the expert's rank
-// (NVLink for a peer, HBM for ourselves).  The last block to finish publishes.
-// ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kRowThreads) dispatch_send_direct_kernel(const __grid_constant__ DevParams p) {
+// Copy one row of nvec 16-byte vectors with all 256 threads, up to four loads in flight each.
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst, int nvec) {
     const int tid = threadIdx.x;
-    const int P = p.T * p.K;
-    const int nvec = p.H >> 3;
-    for (int pair = blockIdx.x; pair < P; pair += gridDim.x) {
-        const int j = p.slot[pair];
-        if (j < 0) continue;
-        const int e = p.idx[pair];
-        const int d = e / p.L, l = e - d * p.L;
-        const int t = pair / p.K, k = pair - t * p.K;
-        const size_t row = ((size_t)l * p.ws + p.rank) * p.T_max + j;
-        const uint4* src = reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec;
-        uint4* dst = reinterpret_cast<uint4*>(p.peer[d] + p.off_rows) + row * nvec;
-        for (int v0 = 0; v0 < nvec; v0 += kRowThreads * 4) {
-            uint4 r[4];
+    for (int v0 = 0; v0 < nvec; v0 += kThreads * 4) {
+        uint4 r[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int v = v0 + u * kRowThreads + tid;
-                if (v < nvec) r[u] = ld_input(src + v);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int v = v0 + u * kRowThreads + tid;
-                if (v < nvec) st_stream(dst + v, r[u]);
-            }
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * kThreads + tid;
+            if (v < nvec) r[u] = ld_input(src + v);
         }
-        if (tid == 0) reinterpret_cast<int*>(p.peer[d] + p.off_meta)[row] = (t << 8) | k;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * kThreads + tid;
+            if (v < nvec) st_stream(dst + v, r[u]);
+        }
     }
-    if (grid_arrive_last(p.tickets + kTicketSend)) publish_dispatch(p);
 }
 
 // ---------------------------------------------------------------------------
-// K3 dispatch receiving half / expert placeholder.  Template switches:
-//   WAIT    wait for every source's dispatch flag of this call (bounded)
-//   SCALE   run the placeholder expert op in place on the valid rows
-//   PUBLISH tell every home rank that this rank's expert outputs are ready
-// The valid rows of all (local expert, source) slabs are flattened with a prefix
-// sum over the received counts so that skewed routing does not idle blocks.
+// Dispatch, sending half.
+// DIRECT: one block per (token, k) pair at a time; the row goes straight into slab
+//   (expert, this rank) on the expert's rank (NVLink for a peer, HBM for ourselves).
+// DEDUP / FP8: one block per (token, destination rank); the row crosses the wire
+//   once per destination into stage[src][t] (FP8: quantised on the fly, one fp32
+//   scale per 128 values) together with K words saying which local experts want it
+//   and at which slot; the receiver fans it out.
+// The block that finishes last publishes counts and flags.
 // ---------------------------------------------------------------------------
-template <typename T, bool WAIT, bool SCALE, bool PUBLISH>
-__global__ void __launch_bounds__(kRowThreads) expert_rows_kernel(const __grid_constant__ DevParams p) {
-    __shared__ int prefix[A2A_MAX_EXPERTS + 1];
+template <typename T, int PAYLOAD>
+__device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& s) {
+    const int tid = threadIdx.x;
+    const int K = p.K, nvec = p.H >> 3;
+    stamp(p, kStampStart);
+    route_build(p, s);
+    stamp(p, kStampRouted);
+    if (PAYLOAD == A2A_PAYLOAD_DIRECT) {
+        const int P = p.T * K;
+        for (int pair = blockIdx.x; pair < P; pair += gridDim.x) {
+            const int t = pair / K, k = pair - t * K;
+            const int e = s.idx[pair];
+            const int j = pair_slot(p, s, t, k, e);
+            if (tid == 0) p.slot[pair] = j;
+            if (j < 0) continue;
+            const int d = e / p.L, l = e - d * p.L;
+            const size_t row = ((size_t)l * p.ws + p.rank) * p.T_max + j;
+            copy_row(reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec,
+                     reinterpret_cast<uint4*>(p.peer[d] + p.off_rows) + row * nvec, nvec);
+            if (tid == 0) reinterpret_cast<int*>(p.peer[d] + p.off_meta)[row] = (t << 8) | k;
+        }
+    } else {
+        const int items = p.T * p.ws;
+        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+            const int t = it / p.ws, d = it - t * p.ws;
+            // which of the token's experts live on d, and where their rows go there
+            int my_meta = -1;
+            if (tid < K) {
+                const int e = s.idx[t * K + tid];
+                const bool in_range = (e >= 0 && e < p.E);
+                const int home = in_range ? e / p.L : 0;  // an out-of-range pair is booked (as dropped) by item d = 0
+                if (home == d) {
+                    const int j = pair_slot(p, s, t, tid, e);
+                    p.slot[(size_t)t * K + tid] = j;
+                    if (j >= 0) my_meta = ((e - d * p.L) << 16) | j;
+                }
+                reinterpret_cast<int*>(p.peer[d] + p.off_stage_meta)[((size_t)p.rank * p.T_max + t) * K + tid] = my_meta;
+            }
+            if (!__syncthreads_or(my_meta >= 0)) continue;
+            uint8_t* wire = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + t) * p.stage_row_bytes;
+            const uint4* src = reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec;
+            if (PAYLOAD == A2A_PAYLOAD_DEDUP) {
+                copy_row(src, reinterpret_cast<uint4*>(wire), nvec);
+            } else {
+                // nvec is a multiple of 16 (H % 128 == 0): the 16 lanes of a scale block are all in or all out
+                for (int v0 = 0; v0 < nvec; v0 += kThreads) {
+                    const int v = v0 + tid;
+                    float f[8];
+                    float amax = 0.f;
+                    if (v < nvec) {
+                        unpack8<T>(ld_input(src + v), f);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+                    }
+#pragma unroll
+                    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    if (v < nvec) {
+                        const float scale = amax > 0.f ? amax / 448.f : 1.f;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = f[i] / scale;
+                        st_stream(reinterpret_cast<uint2*>(wire) + v, pack8_e4m3(f));
+                        if ((v & 15) == 0) reinterpret_cast<float*>(wire + p.H)[v >> 4] = scale;
+                    }
+                }
+            }
+        }
+    }
+    stamp(p, kStampSent);
+    if (grid_arrive_last(p.tickets + kTicketSend)) publish_dispatch(p, s);
+    stamp(p, kStampSendArrived);
+}
+
+// ---------------------------------------------------------------------------
+// Receive side.  Blocks are partitioned over the source ranks (block b serves
+// source b % ws), so rows of a source are processed as soon as THAT source's flag
+// has arrived.  Template switches:
+//   WAIT    wait (bounded) for the source's dispatch flag of this call
+//   FANOUT  DEDUP/FP8 payloads: copy every staged row into the slabs of the local
+//           experts that want it (FP8: dequantise to T first)
+//   SCALE   the placeholder expert op: DIRECT or not FANOUT -> in place on the valid
+//           slab rows; with FANOUT -> applied while fanning out
+//   PUBLISH tell every home rank that this rank's expert outputs are ready
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void scale_slabs_of_source(const DevParams& p, int* pre, int s, int part, int nparts) {
+    const int tid = threadIdx.x;
+    uint8_t* self = p.peer[p.rank];
+    const int* counts = reinterpret_cast<const int*>(self + p.off_counts) + (size_t)s * p.L;
+    for (int l = tid; l < p.L; l += kThreads) {
+        int c = ld_stream(counts + l);
+        if (c < 0 || c > p.T_max) {
+            record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, c);
+            c = 0;
+        }
+        pre[l] = c;
+    }
+    block_exclusive_scan(pre, p.L);
+    const int total = pre[p.L];
+    const int nvec = p.H >> 3;
+    const float scale = (float)(1 + p.rank);
+    uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
+    for (int r = part; r < total; r += nparts) {
+        const int l = upper_slab(pre, p.L, r);
+        const int j = r - pre[l];
+        uint4* row = rows + (((size_t)l * p.ws + s) * p.T_max + j) * nvec;
+        for (int v0 = 0; v0 < nvec; v0 += kThreads * 4) {
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * kThreads + tid;
+                if (v < nvec) q[u] = ld_stream(row + v);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * kThreads + tid;
+                if (v < nvec) st_stream(row + v, scale8<T>(q[u], scale));
+            }
+        }
+    }
+    __syncthreads();  // pre[] is reused by the next source
+}
+
+template <typename T, bool FP8, bool SCALE>
+__device__ __forceinline__ void fanout_source(const DevParams& p, int s, int part, int nparts) {
+    const int tid = threadIdx.x;
+    uint8_t* self = p.peer[p.rank];
+    int Ts = ld_stream(reinterpret_cast<const int*>(self + p.off_src_tokens) + s);
+    if (Ts < 0 || Ts > p.T_max) {
+        record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, Ts);
+        Ts = 0;
+    }
+    const int K = p.K, nvec = p.H >> 3;
+    const float scale = (float)(1 + p.rank);
+    uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
+    int* meta_out = reinterpret_cast<int*>(self + p.off_meta);
+    for (int t = part; t < Ts; t += nparts) {
+        const int* m = reinterpret_cast<const int*>(self + p.off_stage_meta) + ((size_t)s * p.T_max + t) * K;
+        // threads 0..K-1 validate one destination each and record the row's (token, k)
+        int mine = -1;
+        if (tid < K) {
+            mine = ld_stream(m + tid);
+            if (mine >= 0) {
+                const int l = mine >> 16, j = mine & 0xffff;
+                if (l >= p.L || j >= p.T_max) {
+                    record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, mine);
+                    mine = -1;
+                } else {
+                    meta_out[((size_t)l * p.ws + s) * p.T_max + j] = (t << 8) | tid;
+                }
+            }
+        }
+        if (!__syncthreads_or(mine >= 0)) continue;
+        const uint8_t* wire = self + p.off_stage + ((size_t)s * p.T_max + t) * p.stage_row_bytes;
+        for (int v0 = 0; v0 < nvec; v0 += kThreads * 2) {
+            uint4 q[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int v = v0 + u * kThreads + tid;
+                if (v < nvec) {
+                    if (FP8) {
+                        float f[8];
+                        unpack8_e4m3(ld_stream(reinterpret_cast<const uint2*>(wire) + v), f);
+                        const float sc = ld_stream(reinterpret_cast<const float*>(wire + p.H) + (v >> 4));
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] *= sc;
+                        q[u] = pack8<T>(f);  // the received row, rounded to T as the receiver stores it
+                    } else {
+                        q[u] = ld_stream(reinterpret_cast<const uint4*>(wire) + v);
+                    }
+                    if (SCALE) q[u] = scale8<T>(q[u], scale);
+                }
+            }
+            for (int k = 0; k < K; ++k) {
+                const int mk = ld_stream(m + k);
+                if (mk < 0) continue;
+                const int l = mk >> 16, j = mk & 0xffff;
+                if (l >= p.L || j >= p.T_max) continue;
+                uint4* row = rows + (((size_t)l * p.ws + s) * p.T_max + j) * nvec;
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int v = v0 + u * kThreads + tid;
+                    if (v < nvec) st_stream(row + v, q[u]);
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int PAYLOAD, bool WAIT, bool FANOUT, bool SCALE, bool PUBLISH>
+__device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem& sm) {
     __shared__ int s_ok;
     const int tid = threadIdx.x;
     uint8_t* self = p.peer[p.rank];
-    if (tid == 0) s_ok = 1;
-    __syncthreads();
-    if (WAIT) {
-        if (tid < p.ws) {
-            if (!wait_flag(flag_ptr(self, p.off_flags, kFlagDispatch, tid), p.epoch, p, kPhaseRecv, tid)) s_ok = 0;
+    // block b serves source b % ws together with the other blocks of that residue;
+    // a grid smaller than the world size lets each block walk several sources alone
+    const bool many = (int)gridDim.x >= p.ws;
+    const int s_first = many ? (int)blockIdx.x % p.ws : (int)blockIdx.x;
+    const int s_step = many ? p.ws * A2A_MAX_WORLD : (int)gridDim.x;  // many: exactly one source
+    for (int s = s_first; s < p.ws; s += s_step) {
+        const int part = many ? (int)blockIdx.x / p.ws : 0;
+        const int nparts = many ? ((int)gridDim.x - s + p.ws - 1) / p.ws : 1;
+        if (WAIT) {
+            if (tid == 0) s_ok = wait_flag(flag_ptr(self, p.off_flags, kFlagDispatch, s), p.epoch, p, kPhaseRecv, s) ? 1 : 0;
+            __syncthreads();
+            const int ok = s_ok;
+            __syncthreads();
+            if (!ok) break;  // error recorded; the rows of this source are left alone
+            stamp(p, kStampDispatchSeen);
         }
-        __syncthreads();
-    }
-    if (!s_ok) return;  // error recorded; nothing is published, peers run into their own budget
-    const int nslab = p.L * p.ws;  // slab i = l * ws + s
-    if (WAIT || SCALE) {
-        const int* counts = reinterpret_cast<const int*>(self + p.off_counts);
-        for (int i = tid; i < nslab; i += kRowThreads) {
-            const int l = i / p.ws, s = i - l * p.ws;
-            int c = __ldcg(counts + s * p.L + l);
-            if (c < 0 || c > p.T_max) {
-                record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, c);
-                c = 0;
-            }
-            prefix[i] = c;
-        }
-        block_exclusive_scan(prefix, nslab);
-        if (blockIdx.x == 0)
-            for (int l = tid; l < p.L; l += kRowThreads) p.expert_count[l] = prefix[(l + 1) * p.ws] - prefix[l * p.ws];
-    }
-    if (SCALE) {
-        const int total = prefix[nslab];
-        const int nvec = p.H >> 3;
-        const float scale = (float)(1 + p.rank);
-        uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
-        for (int r = blockIdx.x; r < total; r += gridDim.x) {
-            const int i = upper_slab(prefix, nslab, r);
-            const int j = r - prefix[i];
-            uint4* row = rows + ((size_t)i * p.T_max + j) * nvec;
-            for (int v0 = 0; v0 < nvec; v0 += kRowThreads * 4) {
-                uint4 q[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int v = v0 + u * kRowThreads + tid;
-                    if (v < nvec) q[u] = ld_stream(row + v);
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int v = v0 + u * kRowThreads + tid;
-                    if (v < nvec) {
-                        float f[8];
-                        unpack8<T>(q[u], f);
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) f[c] *= scale;
-                        st_stream(row + v, pack8<T>(f));
-                    }
-                }
-            }
+        constexpr bool staged = (PAYLOAD != A2A_PAYLOAD_DIRECT);
+        if (staged && FANOUT) {
+            fanout_source<T, PAYLOAD == A2A_PAYLOAD_FP8, SCALE>(p, s, part, nparts);
+        } else if (SCALE) {
+            scale_slabs_of_source<T>(p, sm.pre, s, part, nparts);
         }
     }
+    stamp(p, kStampExpertDone);
     if (PUBLISH) {
         if (grid_arrive_last(p.tickets + kTicketExpert)) {
-            if (tid < p.ws) st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagExpert, p.rank), p.epoch);
+            // after a timeout the outputs are incomplete: say nothing, the home ranks run into their own budget
+            if (ld_volatile_i32(&p.status->code) != A2A_ERR_TIMEOUT && tid < p.ws)
+                st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagExpert, p.rank), p.epoch);
         }
+        stamp(p, kStampExpertArrived);
     }
 }
 
 // ---------------------------------------------------------------------------
-// K4 combine (pull).  Item = (token, 1024-element chunk); 128 threads, each owns 8
-// consecutive elements: it loads the 16 bytes of each of the token's K expert
-// outputs from the rank that holds them (the slot is known from routing, so there
-// is no metadata to fetch), accumulates float(row) * w[t,k] in fp32 registers in k
-// order and stores 16 bytes of y.  Loads are issued four at a time.
+// Combine (pull).  A warp owns 32 consecutive 16-byte vectors (512 B) of one
+// token's output.  Lane k < K looks up pair (t,k): expert, slot (known from routing,
+// so no metadata is fetched), weight, and waits (bounded) for the expert's rank to
+// have published its outputs; pointer and weight are then broadcast by shuffles and
+// every lane pulls its 16 bytes of each of the K rows from the rank that holds them,
+// four loads in flight, accumulating float(row) * w in fp32 in k order.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const __grid_constant__ DevParams p) {
-    __shared__ const uint4* s_row[A2A_MAX_TOPK];
-    __shared__ float s_w[A2A_MAX_TOPK];
-    __shared__ int s_ok;
-    const int tid = threadIdx.x;
-    if (tid == 0) s_ok = 1;
-    __syncthreads();
-    if (tid < p.ws) {
-        if (!wait_flag(flag_ptr(p.peer[p.rank], p.off_flags, kFlagExpert, tid), p.epoch, p, kPhaseCombine, tid)) s_ok = 0;
-    }
-    __syncthreads();
-    if (!s_ok) return;
-    const int nvec = p.H >> 3;
-    const int nchunk = (p.H + kCombineChunk - 1) / kCombineChunk;
-    const int items = p.T * nchunk;
-    const int K = p.K;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        const int t = item / nchunk, c = item - t * nchunk;
-        __syncthreads();
-        if (tid < K) {
-            const int pair = t * K + tid;
-            const int j = p.slot[pair];
-            const uint4* row = nullptr;
-            float w = 0.f;
+__device__ __forceinline__ void combine_phase(const DevParams& p) {
+    const int lane = threadIdx.x & 31;
+    const int warp = (int)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int nwarps = (int)gridDim.x * (kThreads / 32);
+    const int K = p.K, nvec = p.H >> 3;
+    const int nseg = (nvec + 31) >> 5;
+    const int items = p.T * nseg;
+    for (int item = warp; item < items; item += nwarps) {
+        const int t = item / nseg, seg = item - t * nseg;
+        const int v = seg * 32 + lane;
+        unsigned long long my_row = 0ull;
+        float my_w = 0.f;
+        bool ok = true;
+        if (lane < K) {
+            const size_t pair = (size_t)t * K + lane;
+            const int j = ld_stream(p.slot + pair);
             if (j >= 0) {
-                const int e = p.idx[pair];
+                const int e = __ldg(p.idx + pair);
                 const int d = e / p.L, l = e - d * p.L;
-                row = reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
-                      (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec;
-                w = p.w[pair];
+                my_w = __ldg(p.w + pair);
+                my_row = reinterpret_cast<unsigned long long>(
+                    reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
+                    (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec);
+                ok = wait_flag(flag_ptr(p.peer[p.rank], p.off_flags, kFlagExpert, d), p.epoch, p, kPhaseCombine, d);
             }
-            s_row[tid] = row;
-            s_w[tid] = w;
         }
-        __syncthreads();
-        const int v = c * kCombineThreads + tid;
-        if (v < nvec) {
-            float acc[8];
+        if (!__all_sync(0xffffffffu, ok)) return;  // error recorded; leave the remaining output untouched
+        float acc[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-            for (int k0 = 0; k0 < K; k0 += 4) {
-                uint4 q[4];
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += 4) {
+            uint4 q[4];
+            float w[4];
+            bool have[4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (k0 + u < K && s_row[k0 + u] != nullptr) q[u] = ld_stream(s_row[k0 + u] + v);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (k0 + u < K && s_row[k0 + u] != nullptr) {
-                        float f[8];
-                        unpack8<T>(q[u], f);
-                        const float w = s_w[k0 + u];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[i] = fmaf(f[i], w, acc[i]);
-                    }
+            for (int u = 0; u < 4; ++u) {
+                const int k = (k0 + u < K) ? k0 + u : 0;
+                const unsigned long long row = __shfl_sync(0xffffffffu, my_row, k);
+                w[u] = __shfl_sync(0xffffffffu, my_w, k);
+                have[u] = (k0 + u < K) && row != 0ull && v < nvec;
+                if (have[u]) q[u] = ld_stream(reinterpret_cast<const uint4*>(row) + v);
             }
-            st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v, pack8<T>(acc));
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (have[u]) {
+                    float f[8];
+                    unpack8<T>(q[u], f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(f[i], w[u], acc[i]);
+                }
         }
+        if (v < nvec) st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v, pack8<T>(acc));
     }
+    __syncthreads();
+    stamp(p, kStampCombineDone);
+}
+
+// ---------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------
+extern __shared__ int a2a_dyn_smem[];
+
+// Standalone routing: the slot table and send counts in global memory (what
+// a2a_route promises); the sending kernel recomputes the same values in shared memory.
+__global__ void __launch_bounds__(kThreads) route_kernel(const __grid_constant__ DevParams p) {
+    const BlockSmem s = carve_smem(a2a_dyn_smem, p.E, p.T_max);
+    route_build(p, s);
+    const int P = p.T * p.K;
+    for (int pair = threadIdx.x; pair < P; pair += kThreads) {
+        const int t = pair / p.K, k = pair - t * p.K;
+        p.slot[pair] = pair_slot(p, s, t, k, s.idx[pair]);
+    }
+    for (int e = threadIdx.x; e < p.E; e += kThreads) p.send_counts[e] = s.cnt[e];
+}
+
+template <typename T, int PAYLOAD>
+__global__ void __launch_bounds__(kThreads) send_kernel(const __grid_constant__ DevParams p) {
+    send_phase<T, PAYLOAD>(p, carve_smem(a2a_dyn_smem, p.E, p.T_max));
+}
+
+template <typename T, int PAYLOAD, bool WAIT, bool FANOUT, bool SCALE, bool PUBLISH>
+__global__ void __launch_bounds__(kThreads) expert_kernel(const __grid_constant__ DevParams p) {
+    expert_phase<T, PAYLOAD, WAIT, FANOUT, SCALE, PUBLISH>(p, carve_smem(a2a_dyn_smem, p.E, p.T_max));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant__ DevParams p) {
+    combine_phase<T>(p);
+}
+
+// The whole path in one launch.  Launched cooperatively so that every block is
+// resident: a block that has finished sending waits (bounded) on flags that the
+// last-finishing block of this very grid, or a peer GPU, will set.
+template <typename T, int PAYLOAD>
+__global__ void __launch_bounds__(kThreads) forward_kernel(const __grid_constant__ DevParams p) {
+    const BlockSmem s = carve_smem(a2a_dyn_smem, p.E, p.T_max);
+    send_phase<T, PAYLOAD>(p, s);
+    expert_phase<T, PAYLOAD, true, true, true, true>(p, s);
+    combine_phase<T>(p);
 }
 
 // ---------------------------------------------------------------------------
 // Export: the reference's dispatch return value (reference.py:148) packed from the
 // slabs -- rows of one expert ordered by (source rank, token, k).  Test helper.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kRowThreads) export_dispatch_kernel(const __grid_constant__ DevParams p, int* out_counts, uint4* out_rows,
-                                                                     int* out_meta) {
+__global__ void __launch_bounds__(kThreads) export_dispatch_kernel(const __grid_constant__ DevParams p, int* out_counts,
+                                                                  uint4* out_rows, int* out_meta) {
     __shared__ int prefix[A2A_MAX_EXPERTS + 1];
     const int tid = threadIdx.x;
     uint8_t* self = p.peer[p.rank];
-    const int nslab = p.L * p.ws;
+    const int nslab = p.L * p.ws;  // slab i = l * ws + s
     const int* counts = reinterpret_cast<const int*>(self + p.off_counts);
-    for (int i = tid; i < nslab; i += kRowThreads) {
+    for (int i = tid; i < nslab; i += kThreads) {
         const int l = i / p.ws, s = i - l * p.ws;
-        int c = counts[s * p.L + l];
+        const int c = counts[s * p.L + l];
         prefix[i] = (c < 0 || c > p.T_max) ? 0 : c;
     }
     block_exclusive_scan(prefix, nslab);
     if (blockIdx.x == 0)
-        for (int l = tid; l < p.L; l += kRowThreads) out_counts[l] = prefix[(l + 1) * p.ws] - prefix[l * p.ws];
+        for (int l = tid; l < p.L; l += kThreads) out_counts[l] = prefix[(l + 1) * p.ws] - prefix[l * p.ws];
     const int total = prefix[nslab];
     const int nvec = p.H >> 3;
     const size_t max_recv = (size_t)p.T_max * p.ws;
@@ -299,7 +509,7 @@ __global__ void __launch_bounds__(kRowThreads) export_dispatch_kernel(const __gr
         const int l = i / p.ws, s = i - l * p.ws;
         const size_t in_row = (size_t)i * p.T_max + j;
         const size_t out_row = (size_t)l * max_recv + (prefix[i] - prefix[l * p.ws]) + j;
-        for (int v = tid; v < nvec; v += kRowThreads) out_rows[out_row * nvec + v] = rows[in_row * nvec + v];
+        for (int v = tid; v < nvec; v += kThreads) out_rows[out_row * nvec + v] = rows[in_row * nvec + v];
         if (tid == 0) {
             const int m = meta[in_row];
             int* o = out_meta + out_row * 5;

@@ -36,7 +36,7 @@ enum {
     A2A_ERR_CAPACITY = 2, /* a (source, expert) slab would overflow max_num_tokens rows  */
     A2A_ERR_TIMEOUT = 3,  /* a bounded device-side wait on a peer's flag ran out         */
     A2A_ERR_STATE = 4,    /* call order violated (peers not attached, route missing...)  */
-    A2A_ERR_ROUTING = 5   /* an expert index outside [0, num_experts)                    */
+    A2A_ERR_ROUTING = 5   /* an expert index outside [0, num_experts), or repeated inside a token */
 };
 
 enum { A2A_DTYPE_BF16 = 0, A2A_DTYPE_FP16 = 1 };
@@ -154,6 +154,11 @@ int a2a_combine(a2a_ctx* ctx, const float* topk_weights, void* y, void* stream);
 int a2a_forward(a2a_ctx* ctx, const void* x, const int32_t* topk_idx, const float* topk_weights,
                 void* y, int num_tokens, void* stream);
 
+/* Choose how a2a_forward launches: 1 = the whole path as ONE cooperative kernel
+ * (default where the device supports cooperative launch), 0 = one kernel per phase.
+ * Same results either way.  No counterpart in the reference. */
+int a2a_set_fused(a2a_ctx* ctx, int on);
+
 /* a2a_forward for HOST buffers (pinned for speed): copies x, topk_idx and
  * topk_weights to the device, runs the path, copies y back; all asynchronous
  * on `stream`.  This is the call a host-resident caller of custom_kernel makes. */
@@ -189,6 +194,17 @@ int a2a_copy_route(a2a_ctx* ctx, int32_t* slots_out, int32_t* send_counts_out, v
  * nothing: reads what is there now. */
 int a2a_status(a2a_ctx* ctx, a2a_status_t* out);
 int a2a_status_clear(a2a_ctx* ctx);
+
+/* In-kernel trace.  While enabled, thread 0 of every block stamps the SM cycle counter
+ * at each phase boundary of the launches that follow (slot 0 of a block holds the
+ * nanosecond global timer at its start; then start, routed, sent, send-arrived,
+ * dispatch-seen, expert-done, expert-arrived, combine-done).  a2a_trace_read
+ * synchronises the device and copies the stamps of the most recent traced launch to
+ * host memory: `out` must hold max_blocks * 16 int64.  Both calls synchronise: keep them
+ * off the timed path.  Replaces the profile buffer of the final reference submission
+ * (submission_v9.py:117, :162-184, p2p_state_get_profile). */
+int a2a_trace_enable(a2a_ctx* ctx, int on);
+int a2a_trace_read(a2a_ctx* ctx, int64_t* out, int max_blocks, int* blocks, int* stamps_per_block);
 
 /* Number of kernels this context has launched so far. */
 int64_t a2a_launch_count(a2a_ctx* ctx);

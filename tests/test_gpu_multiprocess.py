@@ -15,6 +15,7 @@ def _worker(rank, ws, port, cases, q):
     import gpu_mode_kernels_b200 as pkg
     from gpu_mode_kernels_b200.all2all import custom_kernel, _CONTEXTS
     from oracle import a2a_oracle as O
+    from parity import check_y
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -23,21 +24,22 @@ def _worker(rank, ws, port, cases, q):
     dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device(f"cuda:{rank}"))
     ok, msg = True, ""
     try:
-        for (E, K, H, T, seed, iters) in cases:
+        for (E, K, H, T, seed, iters, payload) in cases:
             datas = [pkg.generate_input(E, K, H, T, seed=seed, rank=r, world_size=ws, ragged=True) for r in range(ws)]
             cfg = datas[0][0]
-            _, ys = O.simulate(cfg, ws, [d[1] for d in datas])
+            rds_cpu = [d[1] for d in datas]
+            _, ys = O.simulate(cfg, ws, rds_cpu)
             mine = datas[rank][1].to(f"cuda:{rank}")
             y = None
             for _ in range(iters):  # back-to-back, no host sync: epochs and slab reuse under real concurrency
-                y = custom_kernel((cfg, mine, rank, ws))
+                y = custom_kernel((cfg, mine, rank, ws), payload=payload)
             torch.cuda.synchronize()
             for ctx in _CONTEXTS.values():
                 ctx.check()
             try:
-                torch.testing.assert_close(y.cpu().float(), ys[rank].float(), rtol=2e-2, atol=2e-2)
+                check_y(cfg, ws, rds_cpu, {rank: y}, ys, payload, ranks=[rank])
             except AssertionError as e:  # noqa: PERF203
-                ok, msg = False, f"case {(E, K, H, T)}: {e}"
+                ok, msg = False, f"case {(E, K, H, T, payload)}: {e}"
                 break
             dist.barrier()
     except Exception as e:  # noqa: BLE001
@@ -51,7 +53,8 @@ def _worker(rank, ws, port, cases, q):
 def test_custom_kernel_over_ipc(ws):
     if torch.cuda.device_count() < ws:
         pytest.skip(f"needs {ws} GPUs")
-    cases = [(8, 2, 2048, 16, 0, 3), (64, 6, 2048, 64, 2, 30), (256, 8, 7168, 256, 3, 20)]
+    cases = [(8, 2, 2048, 16, 0, 3, "direct"), (64, 6, 2048, 64, 2, 30, "direct"), (256, 8, 7168, 256, 3, 20, "direct"),
+             (64, 6, 2048, 64, 2, 30, "dedup"), (256, 8, 7168, 256, 3, 20, "dedup"), (256, 8, 7168, 256, 4, 20, "fp8")]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, ws, 29800 + ws, cases, q)) for r in range(ws)]
