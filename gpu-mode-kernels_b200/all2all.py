@@ -181,16 +181,15 @@ class A2AContext:
     def clear_status(self) -> None:
         _lib.check(self.lib.a2a_status_clear(self._h))
 
-    STAMPS = ("global_ns", "start", "routed", "sent", "send_arrived", "dispatch_seen", "expert_done",
-              "expert_arrived", "combine_done")
+    STAMPS = ("global_ns", "start", "routed", "sent", "dispatch_seen", "expert_done", "expert_seen", "combine_done")
 
     def trace_enable(self, on: bool = True) -> None:
         """Turn the in-kernel trace on or off (synchronises the device)."""
         _lib.check(self.lib.a2a_trace_enable(self._h, 1 if on else 0))
 
     def trace_read(self) -> torch.Tensor:
-        """Stamps of the most recent traced launch: int64 [blocks, 16] (see STAMPS; cycles, slot 0 in ns)."""
-        buf = torch.zeros(2048, 16, dtype=torch.int64)
+        """Stamps of the most recent traced launch: int64 [blocks, 8] (see STAMPS; cycles, slot 0 in ns)."""
+        buf = torch.zeros(2048, 8, dtype=torch.int64)
         blocks, per = C.c_int(), C.c_int()
         _lib.check(self.lib.a2a_trace_read(self._h, _ptr(buf), 2048, C.byref(blocks), C.byref(per)))
         return buf[: blocks.value]

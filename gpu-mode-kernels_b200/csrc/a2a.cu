@@ -21,33 +21,27 @@ constexpr size_t kMaxSmemBytes = 200 * 1024;  // routing bitmap budget per block
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct Layout {
-    size_t off_rows, off_meta, off_counts, off_src_tokens, off_flags, off_stage, off_stage_meta, total;
+    size_t off_rows, off_meta, off_counts, off_flags, off_stage, total;
     int stage_row_bytes;
 };
 
 Layout make_layout(const a2a_config& c) {
     Layout l{};
     const size_t L = c.num_experts / c.world_size, ws = c.world_size, T = c.max_num_tokens, H = c.hidden_dim;
-    const size_t K = c.experts_per_token;
     size_t off = 0;
     l.off_rows = off;
     off = align_up(off + L * ws * T * H * 2, 256);
-    l.off_meta = off;
+    l.off_meta = off;  // everything from here up to the wire rows starts as zero
     off = align_up(off + L * ws * T * sizeof(int32_t), 256);
     l.off_counts = off;
     off = align_up(off + ws * L * sizeof(int32_t), 256);
-    l.off_src_tokens = off;
-    off = align_up(off + ws * sizeof(int32_t), 256);
     l.off_flags = off;
     off = align_up(off + (size_t)kNumFlagKinds * A2A_MAX_WORLD * kFlagStride * sizeof(uint32_t), 256);
     l.stage_row_bytes = 0;
-    l.off_stage = l.off_stage_meta = off;
+    l.off_stage = off;
     if (c.payload != A2A_PAYLOAD_DIRECT) {
         l.stage_row_bytes = (int)(c.payload == A2A_PAYLOAD_FP8 ? align_up(H + 4 * (H / kFp8Block), 16) : H * 2);
-        l.off_stage = off;
         off = align_up(off + ws * T * (size_t)l.stage_row_bytes, 256);
-        l.off_stage_meta = off;
-        off = align_up(off + ws * T * K * sizeof(int32_t), 256);
     }
     l.total = off;
     return l;
@@ -110,12 +104,11 @@ int validate(const a2a_config& c) {
     if (c.experts_per_token < 1 || c.experts_per_token > A2A_MAX_TOPK || c.experts_per_token > c.num_experts)
         return A2A_ERR_CONFIG;
     if (c.hidden_dim < 8 || c.hidden_dim % 8 != 0) return A2A_ERR_CONFIG;
-    if (c.max_num_tokens < 1 || c.max_num_tokens >= (1 << 22)) return A2A_ERR_CONFIG;
+    if (c.max_num_tokens < 1) return A2A_ERR_CONFIG;
     if (c.dtype != A2A_DTYPE_BF16 && c.dtype != A2A_DTYPE_FP16) return A2A_ERR_CONFIG;
     if (c.payload != A2A_PAYLOAD_DIRECT && c.payload != A2A_PAYLOAD_DEDUP && c.payload != A2A_PAYLOAD_FP8)
         return A2A_ERR_CONFIG;
-    if (c.payload != A2A_PAYLOAD_DIRECT && (c.max_num_tokens > 65535 || c.num_experts / c.world_size > 32767))
-        return A2A_ERR_CONFIG;
+    if (c.max_num_tokens > 65535) return A2A_ERR_CONFIG;  // slots travel in 16 bits
     if (c.payload == A2A_PAYLOAD_FP8 && c.hidden_dim % kFp8Block != 0) return A2A_ERR_CONFIG;
     if (block_smem_ints(c.num_experts, c.max_num_tokens, c.experts_per_token) * sizeof(int) > kMaxSmemBytes) return A2A_ERR_CONFIG;
     if (c.device < 0) return A2A_ERR_CONFIG;
@@ -155,11 +148,12 @@ using KernelFn = void (*)(DevParams);
 template <typename T, int P> struct SendSel { static KernelFn get() { return send_kernel<T, P>; } };
 template <typename T, int P> struct ForwardSel { static KernelFn get() { return forward_kernel<T, P>; } };
 template <typename T, int P> struct ExpertSel {
+    // the receive-side launches of the public phases
     static KernelFn get(bool wait, bool fanout, bool scale, bool publish) {
-        if (wait && fanout && scale && publish) return expert_kernel<T, P, true, true, true, true>;
-        if (wait && fanout && !scale && !publish) return expert_kernel<T, P, true, true, false, false>;
-        if (!wait && !fanout && scale && publish) return expert_kernel<T, P, false, false, true, true>;
-        return expert_kernel<T, P, false, false, false, true>;
+        if (wait && fanout && scale && publish) return expert_kernel<T, P, true, true, true, true>;      // recv + expert fused
+        if (wait && fanout && !scale && !publish) return expert_kernel<T, P, true, true, false, false>;  // dispatch_recv
+        if (!wait && !fanout && scale && publish) return expert_kernel<T, P, false, false, true, true>;  // expert_placeholder
+        return expert_kernel<T, P, false, false, false, true>;                                           // expert_done
     }
 };
 KernelFn combine_fn(const a2a_ctx* c) {
@@ -271,14 +265,15 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
 
     cudaError_t e = cudaMalloc(&c->region, c->lay.total);
     if (e != cudaSuccess) { delete c; return -(int)e; }
-    // flags, counts and metadata start at zero = "epoch 0, nothing received"
-    cudaMemset(c->region + c->lay.off_meta, 0, c->lay.total - c->lay.off_meta);
+    // every flag word starts at zero = "epoch 0, nothing has happened" (the staged wire rows need no clearing)
+    cudaMemset(c->region + c->lay.off_meta, 0, c->lay.off_stage - c->lay.off_meta);
 
-    // local scratch: slot | send_counts | tickets | status | host-path staging
+    // local scratch: slot | send_counts | tickets | seen words | status | trace | host-path staging
     size_t off = 0;
     const size_t o_slot = off;      off = align_up(off + (size_t)T * K * 4, 256);
     const size_t o_send = off;      off = align_up(off + (size_t)E * 4, 256);
     const size_t o_tick = off;      off = align_up(off + 8 * 4, 256);
+    const size_t o_seen = off;      off = align_up(off + 2 * A2A_MAX_WORLD * kFlagStride * 4, 256);
     const size_t o_stat = off;      off = align_up(off + sizeof(a2a_status_t), 256);
     const size_t o_trace = off;     off = align_up(off + (size_t)kTraceBlocks * kNumStamps * 8, 256);
     const size_t o_hx = off;        off = align_up(off + (size_t)T * H * 2, 256);
@@ -295,14 +290,14 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     DevParams& p = c->p;
     p.peer[cfg->rank] = c->region;
     p.off_rows = c->lay.off_rows; p.off_meta = c->lay.off_meta; p.off_counts = c->lay.off_counts;
-    p.off_src_tokens = c->lay.off_src_tokens;
-    p.off_flags = c->lay.off_flags; p.off_stage = c->lay.off_stage; p.off_stage_meta = c->lay.off_stage_meta;
+    p.off_flags = c->lay.off_flags; p.off_stage = c->lay.off_stage;
     p.stage_row_bytes = c->lay.stage_row_bytes;
     p.rank = cfg->rank; p.ws = cfg->world_size; p.E = E; p.K = K; p.H = H; p.T_max = T; p.L = L;
     p.timeout_ns = (long long)c->cfg.timeout_ms * 1000000LL;
     p.slot = reinterpret_cast<int*>(c->scratch + o_slot);
     p.send_counts = reinterpret_cast<int*>(c->scratch + o_send);
     p.tickets = reinterpret_cast<uint32_t*>(c->scratch + o_tick);
+    p.seen = reinterpret_cast<uint32_t*>(c->scratch + o_seen);
     p.status = reinterpret_cast<a2a_status_t*>(c->scratch + o_stat);
     c->trace = reinterpret_cast<long long*>(c->scratch + o_trace);
     c->h_x = c->scratch + o_hx; c->h_y = c->scratch + o_hy;
@@ -410,8 +405,8 @@ int a2a_dispatch_send(a2a_ctx* c, const void* x, void* stream) {
 int a2a_dispatch_recv(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
     DeviceGuard guard(c->cfg.device);
-    // DIRECT: rows are already in place, one block just waits for every source.
-    const int grid = c->cfg.payload == A2A_PAYLOAD_DIRECT ? 1 : expert_grid(c, 4);
+    // DIRECT: the rows are already in place; a minimal grid just waits for every source
+    const int grid = c->cfg.payload == A2A_PAYLOAD_DIRECT ? c->cfg.world_size : expert_grid(c, 4);
     return do_expert(c, true, true, false, false, grid, as_stream(stream));
 }
 
@@ -430,7 +425,7 @@ int a2a_dispatch_recv_expert(a2a_ctx* c, void* stream) {
 int a2a_expert_done(a2a_ctx* c, void* stream) {
     if (c == nullptr) return A2A_ERR_CONFIG;
     DeviceGuard guard(c->cfg.device);
-    return do_expert(c, false, false, false, true, 1, as_stream(stream));
+    return do_expert(c, false, false, false, true, expert_grid(c, 1), as_stream(stream));
 }
 
 int a2a_combine(a2a_ctx* c, const float* w, void* y, void* stream) {

@@ -2,16 +2,28 @@
 // system-scope flag operations with bounded waits, 16-byte row access, block scan,
 // element conversions (bf16 / fp16 / fp8 e4m3).
 //
-// Memory-ordering protocol used throughout (producer on GPU A, consumer on GPU B):
-//   producer threads: plain stores to B's memory -> block barrier -> ONE thread per
-//   block: __threadfence_system() and an atomic ticket on A; the block that draws the
-//   last ticket fences again and writes the flag with st.release.sys into B's memory.
-//   (One fence per block, not per thread: with a system fence in every thread the membar
-//   stall was the largest stall reason of the sending kernel, 53 of ~130 cycles per issue.)
-//   consumer: ld.acquire.sys on its own flag until it carries this call's epoch
-//   (bounded by a wall-clock budget), block/warp barrier, then plain loads.
-// Flags carry a monotonically increasing call number ("epoch"), are never reset,
-// and every (source, destination) pair has its own flag word on its own 128-byte line.
+// Synchronisation.  System-scope fences are the scarce resource on this machine: a
+// B200 retires them at roughly 100-150 per microsecond for the whole chip (740 blocks
+// executing one fence.sys each take ~6.5 us; four each take ~31 us), whereas gpu-scope
+// fences are nearly free (a fence.gpu after every row costs ~1 us over 2048 rows).  So:
+//   * blocks of one GPU synchronise among themselves at gpu scope only: after its last
+//     store of a phase a block meets at a barrier, ONE thread fences at gpu scope and draws
+//     an atomic ticket;
+//   * the block that draws the last ticket is the phase's publisher: for the consumers on
+//     its own GPU a gpu-scope release of a local word, for the peers one fence.sys and then
+//     relaxed system-scope stores of this call's epoch into one flag word per peer;
+//   * on the consumer GPU one "watcher" thread per flag polls it with relaxed system-scope
+//     loads (an acquire load per poll would run a fence per iteration), fences once at
+//     system scope when it has seen the epoch, and re-publishes it in a local word with a
+//     gpu-scope release; everybody else waits on the local word at gpu scope.
+// The PTX memory model makes causality order transitive across edges of different scope,
+// so a row stored by any block of GPU A is visible to any block of GPU B that has seen
+// B's local word, with 2*world system fences per GPU and call instead of thousands (none
+// at all on a single GPU).
+// Flags carry a monotonically increasing call number ("epoch"), are never reset, and
+// every (source, destination) pair has its own flag word on its own 128-byte line.
+// Every wait is bounded by a wall-clock budget; on expiry the kernel records
+// A2A_ERR_TIMEOUT and returns normally.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -29,12 +41,12 @@ constexpr int kFlagStride = 32;  // uint32 words between two flags = 128 bytes
 constexpr int kFp8Block = 128;   // elements sharing one fp32 scale
 enum FlagKind : int { kFlagDispatch = 0, kFlagExpert = 1, kFlagBarrier = 2, kNumFlagKinds = 3 };
 enum Phase : int { kPhaseRoute = 1, kPhaseSend = 2, kPhaseRecv = 3, kPhaseExpert = 4, kPhaseCombine = 5, kPhaseBarrier = 6 };
-enum Ticket : int { kTicketSend = 0, kTicketExpert = 1 };
 // In-kernel trace: thread 0 of every block stamps these points with the SM cycle counter
 // (slot 0 additionally holds the nanosecond global timer so blocks can be aligned).
+enum Ticket : int { kTicketSend = 0, kTicketExpert = 1 };
 enum Stamp : int {
-    kStampGlobalNs = 0, kStampStart, kStampRouted, kStampSent, kStampSendArrived, kStampDispatchSeen,
-    kStampExpertDone, kStampExpertArrived, kStampCombineDone, kNumStamps = 16
+    kStampGlobalNs = 0, kStampStart, kStampRouted, kStampSent, kStampDispatchSeen, kStampExpertDone,
+    kStampExpertSeen, kStampCombineDone, kNumStamps = 8
 };
 
 // Everything a kernel needs, passed by value (lives in the constant bank).
@@ -44,10 +56,8 @@ struct DevParams {
     size_t off_rows;        // [L][ws][T_max][H] elements: slab (l, src) holds the rows src sent to local expert l
     size_t off_meta;        // [L][ws][T_max] int32: (token << 8) | k of every row
     size_t off_counts;      // [ws][L] int32: rows source s sent to local expert l in the current call
-    size_t off_src_tokens;  // [ws] int32: tokens source s holds in the current call
-    size_t off_flags;       // [kNumFlagKinds][A2A_MAX_WORLD][kFlagStride] uint32 epochs
+    size_t off_flags;       // [kNumFlagKinds][A2A_MAX_WORLD][kFlagStride] u32 epochs, written by the peers
     size_t off_stage;       // [ws][T_max][stage_row_bytes]: one wire row per (source, token)   (DEDUP / FP8)
-    size_t off_stage_meta;  // [ws][T_max][K] int32: (local_expert << 16 | slot) or -1 per k   (DEDUP / FP8)
     int stage_row_bytes;
     int rank, ws, E, K, H, T_max, L;
     int T;                  // tokens of this rank in the current call
@@ -56,7 +66,8 @@ struct DevParams {
     // local scratch of this rank
     int* slot;              // [T_max*K] slot of pair (t,k) inside slab (expert, this rank), -1 = dropped
     int* send_counts;       // [E]
-    uint32_t* tickets;      // [8] block-arrival counters, one per phase
+    uint32_t* tickets;      // [2] block-arrival counters, one per publishing phase
+    uint32_t* seen;         // [2][A2A_MAX_WORLD][kFlagStride] local re-publication of the peers' dispatch / expert flags
     a2a_status_t* status;
     long long* trace;       // [blocks][kNumStamps] or nullptr when tracing is off
     // caller tensors of the current call
@@ -84,6 +95,32 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+
+// Strong (L1-bypassing) load without ordering: what a spin loop polls with.  Polling with
+// acquire loads would execute a fence per iteration in every waiting block.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -124,26 +161,39 @@ __device__ __forceinline__ uint32_t* flag_ptr(uint8_t* region_base, size_t off_f
     return reinterpret_cast<uint32_t*>(region_base + off_flags) + ((size_t)kind * A2A_MAX_WORLD + index) * kFlagStride;
 }
 
-// Spin until *flag has reached `epoch` (wrap-safe).  Gives up after timeout_ns, or as
-// soon as any thread of this rank has recorded a timeout (so that one missing peer costs
-// one budget, not one per waiter), and returns false.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
-    if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    const long long t0 = global_ns();
+__device__ __forceinline__ void record_timeout(const DevParams& p, int phase, int peer, uint32_t epoch) {
+    // a timeout outranks whatever was recorded before: the other waiters key on it
+    if (atomicExch(&p.status->code, A2A_ERR_TIMEOUT) != A2A_ERR_TIMEOUT) {
+        p.status->rank = p.rank;
+        p.status->peer = peer;
+        p.status->phase = phase;
+        p.status->epoch = epoch;
+        p.status->detail = 0;
+        __threadfence();
+    }
+}
+
+// Spin until the epoch read through `load()` has reached `epoch` (wrap-safe), then run
+// `acquire()` (the fence of the right scope).  Gives up after timeout_ns, or as soon as
+// any thread of this rank has recorded a timeout (one missing peer costs one budget, not
+// one per waiter), and returns false.
+template <typename Load, typename Acquire>
+__device__ __forceinline__ bool wait_epoch(Load load, Acquire acquire, uint32_t epoch, const DevParams& p, int phase,
+                                           int peer) {
+    long long t0 = 0;
     unsigned backoff = 32;
-    for (;;) {
-        if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    for (int spins = 0;; ++spins) {
+        if ((int32_t)(load() - epoch) >= 0) {
+            acquire();  // relaxed load + fence = acquire
+            return true;
+        }
+        if (spins == 0) {
+            t0 = global_ns();
+            continue;
+        }
         if (ld_volatile_i32(&p.status->code) == A2A_ERR_TIMEOUT) return false;
         if (global_ns() - t0 > p.timeout_ns) {
-            // a timeout outranks whatever was recorded before: the other waiters key on it
-            if (atomicExch(&p.status->code, A2A_ERR_TIMEOUT) != A2A_ERR_TIMEOUT) {
-                p.status->rank = p.rank;
-                p.status->peer = peer;
-                p.status->phase = phase;
-                p.status->epoch = epoch;
-                p.status->detail = 0;
-                __threadfence();
-            }
+            record_timeout(p, phase, peer, epoch);
             return false;
         }
         __nanosleep(backoff);
@@ -151,20 +201,41 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
     }
 }
 
-// All threads of the block call this after their last store of a phase.  Returns true
-// in exactly one block of the grid: the one that arrived last, after which every store
-// of every block is ordered before whatever that block publishes next.
+// A flag another GPU writes: system scope.
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
+    return wait_epoch([flag] { return ld_relaxed_sys(flag); }, [] { fence_acq_rel_sys(); }, epoch, p, phase, peer);
+}
+
+// A word a thread of this GPU writes: gpu scope.
+__device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
+    return wait_epoch([flag] { return ld_relaxed_gpu(flag); }, [] { fence_acq_rel_gpu(); }, epoch, p, phase, peer);
+}
+
+__device__ __forceinline__ uint32_t* seen_ptr(const DevParams& p, int kind, int index) {
+    return p.seen + ((size_t)kind * A2A_MAX_WORLD + index) * kFlagStride;
+}
+
+// Watcher duty: wait for peer `index`'s flag of `kind` at system scope, then hand it to
+// the rest of this GPU through the local word.  On a timeout nothing is handed on and
+// the local waiters run into the recorded timeout.
+__device__ __forceinline__ bool watch_and_republish(const DevParams& p, int kind, int index, int phase) {
+    const bool ok = wait_flag_sys(flag_ptr(p.peer[p.rank], p.off_flags, kind, index), p.epoch, p, phase, index);
+    if (ok) st_release_gpu(seen_ptr(p, kind, index), p.epoch);
+    return ok;
+}
+
+// All threads of the block call this after their last store of a phase.  Returns true in
+// exactly one block of the grid: the one that arrived last.  The caller of that block
+// must fence (system scope) before it publishes; every store of every block is then
+// ordered before the publication.
 __device__ __forceinline__ bool grid_arrive_last(uint32_t* ticket) {
     __shared__ int s_last;
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence_system();
+        __threadfence();  // gpu scope: cheap, and enough between blocks of one GPU
         const uint32_t t = atomicAdd(ticket, 1u);
         const int last = (t == gridDim.x - 1);
-        if (last) {
-            *ticket = 0;  // everyone has arrived: re-arm for the next launch
-            __threadfence_system();
-        }
+        if (last) *ticket = 0;  // everyone has arrived: re-arm for the next launch
         s_last = last;
     }
     __syncthreads();

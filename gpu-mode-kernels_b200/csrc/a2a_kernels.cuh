@@ -3,7 +3,7 @@
 // phase entry points) or back to back inside ONE cooperative kernel (a2a_forward).
 // Hand-written for sm_100a.  Every phase is bound by NVLink or HBM bandwidth (there
 // is no contraction on this path), so the work is 16-byte vector traffic spread over
-// a grid that is a multiple of the SM count, with flag traffic kept off the row path.
+// a grid that is a multiple of the SM count, with as few system-scope fences as possible.
 #pragma once
 
 #include "a2a_device.cuh"
@@ -15,7 +15,7 @@ namespace a2a {
 //   bits [Wc][E]  bit t%32 of word t/32 set iff token t of this rank uses expert e
 //   wpre [Wc][E]  number of set bits in the words before w (exclusive scan over w)
 //   cnt  [E]      tokens using expert e = rows this rank sends to e
-//   pre  [E+2]    scratch for the receive-side prefix sums
+//   pre  [max(E+2, Wmax+1)] scratch of the receive side: slab prefix sums or the token mask
 //   idx  [T*K]    this rank's top-k expert indices (one coalesced pass over global memory;
 //                 every later look-up, including the repeat check, is a shared-memory read)
 // Wc = ceil(T/32) words of the current call; the allocation is sized for T_max.
@@ -28,9 +28,14 @@ struct BlockSmem {
     int* idx;
 };
 
+__host__ __device__ inline size_t pre_ints(int E, int T_max) {
+    const size_t W = (size_t)(T_max + 31) / 32;
+    return (size_t)E + 2 > W + 1 ? (size_t)E + 2 : W + 1;
+}
+
 __host__ __device__ inline size_t block_smem_ints(int E, int T_max, int K) {
     const size_t W = (size_t)(T_max + 31) / 32;
-    return 2 * W * E + E + (size_t)E + 2 + (size_t)T_max * K;
+    return 2 * W * E + E + pre_ints(E, T_max) + (size_t)T_max * K;
 }
 
 __device__ __forceinline__ BlockSmem carve_smem(int* base, int E, int T_max) {
@@ -40,7 +45,7 @@ __device__ __forceinline__ BlockSmem carve_smem(int* base, int E, int T_max) {
     s.wpre = base + W * E;
     s.cnt = base + 2 * W * E;
     s.pre = s.cnt + E;
-    s.idx = s.pre + E + 2;
+    s.idx = s.pre + pre_ints(E, T_max);
     return s;
 }
 
@@ -70,14 +75,19 @@ __device__ __forceinline__ void route_build(const DevParams& p, const BlockSmem&
     for (int pair = tid; pair < P; pair += kThreads) s.idx[pair] = __ldg(p.idx + pair);
     for (int i = tid; i < Wc * E; i += kThreads) s.bits[i] = 0u;
     __syncthreads();
-    for (int pair = tid; pair < P; pair += kThreads) {
-        const int e = s.idx[pair];
-        const int t = pair / K, k = pair - t * K;
-        if (!pair_is_valid(p, s, t, k, e)) {
-            record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
-            continue;
+    // one token per thread: no division, K consecutive indices (one or two 32-byte sectors)
+    for (int t = tid; t < p.T; t += kThreads) {
+        const int* row = p.idx + (size_t)t * K;
+        const unsigned bit = 1u << (t & 31);
+        unsigned* word = s.bits + (t >> 5) * E;
+        for (int k = 0; k < K; ++k) {
+            const int e = __ldg(row + k);
+            if (e < 0 || e >= E) {
+                record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+            } else if (atomicOr(word + e, bit) & bit) {  // only this thread sets this bit: a repeat inside the token
+                record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+            }
         }
-        atomicOr(&s.bits[(t >> 5) * E + e], 1u << (t & 31));
     }
     __syncthreads();
     for (int e = tid; e < E; e += kThreads) {
@@ -98,20 +108,29 @@ __device__ __forceinline__ int pair_slot(const DevParams& p, const BlockSmem& s,
     return s.wpre[w * p.E + e] + __popc(s.bits[w * p.E + e] & ((1u << (t & 31)) - 1u));
 }
 
-// Publish this rank's per-expert counts, its token count and the dispatch flag to
-// every peer.  Called by all threads of the one block that arrived last.
-__device__ __forceinline__ void publish_dispatch(const DevParams& p, const BlockSmem& s) {
+// Publication of a phase by all threads of the block that arrived last.  Our own rank
+// is served first and at gpu scope (its consumers are blocks of this GPU); the peers
+// get ONE system fence, then this call's epoch in their flag word of `kind`.
+__device__ __forceinline__ void publish_flags(const DevParams& p, int kind) {
     const int tid = threadIdx.x;
-    for (int e = tid; e < p.E; e += kThreads) {
+    __syncthreads();  // whatever the block wrote for this publication has been issued
+    if (tid == 0) st_release_gpu(seen_ptr(p, kind, p.rank), p.epoch);  // fence.gpu + store
+    if (p.ws > 1) {
+        if (tid == 0) __threadfence_system();  // orders every block's rows (seen through the tickets) for the peers
+        __syncthreads();
+        if (tid < p.ws && tid != p.rank) st_relaxed_sys(flag_ptr(p.peer[tid], p.off_flags, kind, p.rank), p.epoch);
+    }
+}
+
+// Dispatch publication: per destination the row count of every (this source, local
+// expert) slab, then the flags.
+__device__ __forceinline__ void publish_dispatch(const DevParams& p, const BlockSmem& s) {
+    for (int e = threadIdx.x; e < p.E; e += kThreads) {
         const int d = e / p.L, l = e - d * p.L;
         reinterpret_cast<int*>(p.peer[d] + p.off_counts)[p.rank * p.L + l] = s.cnt[e];
         p.send_counts[e] = s.cnt[e];
     }
-    if (tid < p.ws) reinterpret_cast<int*>(p.peer[tid] + p.off_src_tokens)[p.rank] = p.T;
-    __syncthreads();
-    if (tid == 0) __threadfence_system();
-    __syncthreads();
-    if (tid < p.ws) st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagDispatch, p.rank), p.epoch);
+    publish_flags(p, kFlagDispatch);
 }
 
 // Copy one row of nvec 16-byte vectors with all 256 threads, up to four loads in flight each.
@@ -133,13 +152,13 @@ __device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* _
 }
 
 // ---------------------------------------------------------------------------
-// Dispatch, sending half.
+// Dispatch, sending half.  Never waits.
 // DIRECT: one block per (token, k) pair at a time; the row goes straight into slab
 //   (expert, this rank) on the expert's rank (NVLink for a peer, HBM for ourselves).
 // DEDUP / FP8: one block per (token, destination rank); the row crosses the wire
 //   once per destination into stage[src][t] (FP8: quantised on the fly, one fp32
-//   scale per 128 values) together with K words saying which local experts want it
-//   and at which slot; the receiver fans it out.
+//   scale per 128 values); every slab row that wants it gets its (token, k) word,
+//   through which the receiver finds the wire row when it fans out.
 // The block that finishes last publishes counts and flags.
 // ---------------------------------------------------------------------------
 template <typename T, int PAYLOAD>
@@ -167,8 +186,9 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
         const int items = p.T * p.ws;
         for (int it = blockIdx.x; it < items; it += gridDim.x) {
             const int t = it / p.ws, d = it - t * p.ws;
-            // which of the token's experts live on d, and where their rows go there
-            int my_meta = -1;
+            // which of the token's experts live on d: each of them gets its slab row's (token, k)
+            // word there; the row itself crosses the wire once
+            int hit = 0;
             if (tid < K) {
                 const int e = s.idx[t * K + tid];
                 const bool in_range = (e >= 0 && e < p.E);
@@ -176,11 +196,14 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
                 if (home == d) {
                     const int j = pair_slot(p, s, t, tid, e);
                     p.slot[(size_t)t * K + tid] = j;
-                    if (j >= 0) my_meta = ((e - d * p.L) << 16) | j;
+                    if (j >= 0) {
+                        const size_t row = ((size_t)(e - d * p.L) * p.ws + p.rank) * p.T_max + j;
+                        reinterpret_cast<int*>(p.peer[d] + p.off_meta)[row] = (t << 8) | tid;
+                        hit = 1;
+                    }
                 }
-                reinterpret_cast<int*>(p.peer[d] + p.off_stage_meta)[((size_t)p.rank * p.T_max + t) * K + tid] = my_meta;
             }
-            if (!__syncthreads_or(my_meta >= 0)) continue;
+            if (!__syncthreads_or(hit)) continue;  // nothing of this token lives on d
             uint8_t* wire = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + t) * p.stage_row_bytes;
             const uint4* src = reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec;
             if (PAYLOAD == A2A_PAYLOAD_DEDUP) {
@@ -211,22 +234,30 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
     }
     stamp(p, kStampSent);
     if (grid_arrive_last(p.tickets + kTicketSend)) publish_dispatch(p, s);
-    stamp(p, kStampSendArrived);
 }
 
 // ---------------------------------------------------------------------------
-// Receive side.  Blocks are partitioned over the source ranks (block b serves
-// source b % ws), so rows of a source are processed as soon as THAT source's flag
-// has arrived.  Template switches:
+// Receive side.  Blocks are partitioned over the source ranks (block b serves source
+// b % ws), so the rows of a source are processed as soon as THAT source's flag has
+// arrived.  The first block of every source is its watcher (system scope); the others
+// wait on the local word.  Template switches:
 //   WAIT    wait (bounded) for the source's dispatch flag of this call
-//   FANOUT  DEDUP/FP8 payloads: copy every staged row into the slabs of the local
-//           experts that want it (FP8: dequantise to T first)
-//   SCALE   the placeholder expert op: DIRECT or not FANOUT -> in place on the valid
-//           slab rows; with FANOUT -> applied while fanning out
+//   FANOUT  DEDUP/FP8 payloads: fill every valid slab row from the wire row of its token
+//           (FP8: dequantise to T first)
+//   SCALE   the placeholder expert op on the valid slab rows: in place, or with FANOUT
+//           applied while fanning out
 //   PUBLISH tell every home rank that this rank's expert outputs are ready
 // ---------------------------------------------------------------------------
-template <typename T>
-__device__ __forceinline__ void scale_slabs_of_source(const DevParams& p, int* pre, int s, int part, int nparts) {
+// The valid rows of source s, flattened over the local experts with a prefix sum of the
+// counts so that skewed routing does not idle blocks; one block per row at a time.
+//   FANOUT (staged payloads): the row's content comes from the wire row of its token
+//          (found through the row's (token, k) word), FP8: dequantised and rounded to T;
+//   SCALE: the placeholder expert op, T(float(row) * (1 + rank)), on the way.
+// Without FANOUT the row is read from the slab itself (in place).
+template <typename T, int PAYLOAD, bool FANOUT, bool SCALE>
+__device__ __forceinline__ void rows_of_source(const DevParams& p, int* pre, int s, int part, int nparts) {
+    constexpr bool from_wire = FANOUT && PAYLOAD != A2A_PAYLOAD_DIRECT;
+    constexpr bool fp8 = from_wire && PAYLOAD == A2A_PAYLOAD_FP8;
     const int tid = threadIdx.x;
     uint8_t* self = p.peer[p.rank];
     const int* counts = reinterpret_cast<const int*>(self + p.off_counts) + (size_t)s * p.L;
@@ -243,88 +274,45 @@ __device__ __forceinline__ void scale_slabs_of_source(const DevParams& p, int* p
     const int nvec = p.H >> 3;
     const float scale = (float)(1 + p.rank);
     uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
+    const int* meta = reinterpret_cast<const int*>(self + p.off_meta);
     for (int r = part; r < total; r += nparts) {
         const int l = upper_slab(pre, p.L, r);
         const int j = r - pre[l];
-        uint4* row = rows + (((size_t)l * p.ws + s) * p.T_max + j) * nvec;
+        const size_t ri = ((size_t)l * p.ws + s) * p.T_max + j;
+        uint4* row = rows + ri * nvec;
+        const uint8_t* wire = nullptr;
+        if (from_wire) {
+            int t = ld_stream(meta + ri) >> 8;
+            if (t < 0 || t >= p.T_max) {
+                record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, t);
+                continue;
+            }
+            wire = self + p.off_stage + ((size_t)s * p.T_max + t) * p.stage_row_bytes;
+        }
         for (int v0 = 0; v0 < nvec; v0 += kThreads * 4) {
             uint4 q[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int v = v0 + u * kThreads + tid;
-                if (v < nvec) q[u] = ld_stream(row + v);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int v = v0 + u * kThreads + tid;
-                if (v < nvec) st_stream(row + v, scale8<T>(q[u], scale));
-            }
-        }
-    }
-    __syncthreads();  // pre[] is reused by the next source
-}
-
-template <typename T, bool FP8, bool SCALE>
-__device__ __forceinline__ void fanout_source(const DevParams& p, int s, int part, int nparts) {
-    const int tid = threadIdx.x;
-    uint8_t* self = p.peer[p.rank];
-    int Ts = ld_stream(reinterpret_cast<const int*>(self + p.off_src_tokens) + s);
-    if (Ts < 0 || Ts > p.T_max) {
-        record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, Ts);
-        Ts = 0;
-    }
-    const int K = p.K, nvec = p.H >> 3;
-    const float scale = (float)(1 + p.rank);
-    uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
-    int* meta_out = reinterpret_cast<int*>(self + p.off_meta);
-    for (int t = part; t < Ts; t += nparts) {
-        const int* m = reinterpret_cast<const int*>(self + p.off_stage_meta) + ((size_t)s * p.T_max + t) * K;
-        // threads 0..K-1 validate one destination each and record the row's (token, k)
-        int mine = -1;
-        if (tid < K) {
-            mine = ld_stream(m + tid);
-            if (mine >= 0) {
-                const int l = mine >> 16, j = mine & 0xffff;
-                if (l >= p.L || j >= p.T_max) {
-                    record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, mine);
-                    mine = -1;
-                } else {
-                    meta_out[((size_t)l * p.ws + s) * p.T_max + j] = (t << 8) | tid;
-                }
-            }
-        }
-        if (!__syncthreads_or(mine >= 0)) continue;
-        const uint8_t* wire = self + p.off_stage + ((size_t)s * p.T_max + t) * p.stage_row_bytes;
-        for (int v0 = 0; v0 < nvec; v0 += kThreads * 2) {
-            uint4 q[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int v = v0 + u * kThreads + tid;
                 if (v < nvec) {
-                    if (FP8) {
+                    if (fp8) {
                         float f[8];
                         unpack8_e4m3(ld_stream(reinterpret_cast<const uint2*>(wire) + v), f);
                         const float sc = ld_stream(reinterpret_cast<const float*>(wire + p.H) + (v >> 4));
 #pragma unroll
                         for (int i = 0; i < 8; ++i) f[i] *= sc;
                         q[u] = pack8<T>(f);  // the received row, rounded to T as the receiver stores it
-                    } else {
+                    } else if (from_wire) {
                         q[u] = ld_stream(reinterpret_cast<const uint4*>(wire) + v);
+                    } else {
+                        q[u] = ld_stream(row + v);
                     }
-                    if (SCALE) q[u] = scale8<T>(q[u], scale);
                 }
             }
-            for (int k = 0; k < K; ++k) {
-                const int mk = ld_stream(m + k);
-                if (mk < 0) continue;
-                const int l = mk >> 16, j = mk & 0xffff;
-                if (l >= p.L || j >= p.T_max) continue;
-                uint4* row = rows + (((size_t)l * p.ws + s) * p.T_max + j) * nvec;
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int v = v0 + u * kThreads + tid;
-                    if (v < nvec) st_stream(row + v, q[u]);
-                }
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * kThreads + tid;
+                if (v < nvec) st_stream(row + v, SCALE ? scale8<T>(q[u], scale) : q[u]);
             }
         }
     }
@@ -332,9 +320,8 @@ __device__ __forceinline__ void fanout_source(const DevParams& p, int s, int par
 
 template <typename T, int PAYLOAD, bool WAIT, bool FANOUT, bool SCALE, bool PUBLISH>
 __device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem& sm) {
-    __shared__ int s_ok;
+    __shared__ int s_seen;
     const int tid = threadIdx.x;
-    uint8_t* self = p.peer[p.rank];
     // block b serves source b % ws together with the other blocks of that residue;
     // a grid smaller than the world size lets each block walk several sources alone
     const bool many = (int)gridDim.x >= p.ws;
@@ -344,36 +331,39 @@ __device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem
         const int part = many ? (int)blockIdx.x / p.ws : 0;
         const int nparts = many ? ((int)gridDim.x - s + p.ws - 1) / p.ws : 1;
         if (WAIT) {
-            if (tid == 0) s_ok = wait_flag(flag_ptr(self, p.off_flags, kFlagDispatch, s), p.epoch, p, kPhaseRecv, s) ? 1 : 0;
+            // part 0 watches a peer's flag at system scope and hands it on; the rest, and everybody
+            // for our own rank (whose publisher writes the local word itself), wait locally
+            if (tid == 0)
+                s_seen = (part == 0 && s != p.rank
+                              ? watch_and_republish(p, kFlagDispatch, s, kPhaseRecv)
+                              : wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), p.epoch, p, kPhaseRecv, s)) ? 1 : 0;
             __syncthreads();
-            const int ok = s_ok;
+            const int seen = s_seen;
             __syncthreads();
-            if (!ok) break;  // error recorded; the rows of this source are left alone
+            if (!seen) break;  // timeout recorded; the rows of this source are left alone
             stamp(p, kStampDispatchSeen);
         }
         constexpr bool staged = (PAYLOAD != A2A_PAYLOAD_DIRECT);
-        if (staged && FANOUT) {
-            fanout_source<T, PAYLOAD == A2A_PAYLOAD_FP8, SCALE>(p, s, part, nparts);
-        } else if (SCALE) {
-            scale_slabs_of_source<T>(p, sm.pre, s, part, nparts);
-        }
+        if ((staged && FANOUT) || SCALE) rows_of_source<T, PAYLOAD, FANOUT, SCALE>(p, sm.pre, s, part, nparts);
+        __syncthreads();  // sm.pre is reused by the next source
     }
     stamp(p, kStampExpertDone);
     if (PUBLISH) {
         if (grid_arrive_last(p.tickets + kTicketExpert)) {
             // after a timeout the outputs are incomplete: say nothing, the home ranks run into their own budget
-            if (ld_volatile_i32(&p.status->code) != A2A_ERR_TIMEOUT && tid < p.ws)
-                st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagExpert, p.rank), p.epoch);
+            if (tid == 0) s_seen = (ld_volatile_i32(&p.status->code) != A2A_ERR_TIMEOUT) ? 1 : 0;
+            __syncthreads();
+            if (s_seen) publish_flags(p, kFlagExpert);
         }
-        stamp(p, kStampExpertArrived);
     }
 }
 
 // ---------------------------------------------------------------------------
 // Combine (pull).  A warp owns 32 consecutive 16-byte vectors (512 B) of one
 // token's output.  Lane k < K looks up pair (t,k): expert, slot (known from routing,
-// so no metadata is fetched), weight, and waits (bounded) for the expert's rank to
-// have published its outputs; pointer and weight are then broadcast by shuffles and
+// so no metadata is fetched), weight, and waits (bounded) until the expert's rank has
+// published its outputs -- warp d of the grid is the watcher of rank d's flag, the
+// others wait on the local word.  Pointer and weight are then broadcast by shuffles and
 // every lane pulls its 16 bytes of each of the K rows from the rank that holds them,
 // four loads in flight, accumulating float(row) * w in fp32 in k order.
 // ---------------------------------------------------------------------------
@@ -385,6 +375,9 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
     const int K = p.K, nvec = p.H >> 3;
     const int nseg = (nvec + 31) >> 5;
     const int items = p.T * nseg;
+    if (warp < p.ws && warp != p.rank && lane == 0) watch_and_republish(p, kFlagExpert, warp, kPhaseCombine);
+    __syncwarp();
+    unsigned ready = 0u;  // ranks this lane has already seen ready
     for (int item = warp; item < items; item += nwarps) {
         const int t = item / nseg, seg = item - t * nseg;
         const int v = seg * 32 + lane;
@@ -401,10 +394,14 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
                 my_row = reinterpret_cast<unsigned long long>(
                     reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
                     (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec);
-                ok = wait_flag(flag_ptr(p.peer[p.rank], p.off_flags, kFlagExpert, d), p.epoch, p, kPhaseCombine, d);
+                if (!((ready >> d) & 1u)) {
+                    ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), p.epoch, p, kPhaseCombine, d);
+                    ready |= 1u << d;
+                }
             }
         }
-        if (!__all_sync(0xffffffffu, ok)) return;  // error recorded; leave the remaining output untouched
+        if (!__all_sync(0xffffffffu, ok)) return;  // timeout recorded; leave the remaining output untouched
+        if (item == warp) stamp(p, kStampExpertSeen);
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -469,7 +466,7 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
 }
 
 // The whole path in one launch.  Launched cooperatively so that every block is
-// resident: a block that has finished sending waits (bounded) on flags that the
+// resident: a block that has finished sending waits (bounded) on words that the
 // last-finishing block of this very grid, or a peer GPU, will set.
 template <typename T, int PAYLOAD>
 __global__ void __launch_bounds__(kThreads) forward_kernel(const __grid_constant__ DevParams p) {
@@ -528,7 +525,7 @@ __global__ void barrier_kernel(const __grid_constant__ DevParams p, uint32_t bar
     if (tid < p.ws) {
         __threadfence_system();
         st_release_sys(flag_ptr(p.peer[tid], p.off_flags, kFlagBarrier, p.rank), barrier_epoch);
-        wait_flag(flag_ptr(p.peer[p.rank], p.off_flags, kFlagBarrier, tid), barrier_epoch, p, kPhaseBarrier, tid);
+        wait_flag_sys(flag_ptr(p.peer[p.rank], p.off_flags, kFlagBarrier, tid), barrier_epoch, p, kPhaseBarrier, tid);
     }
 }
 

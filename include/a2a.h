@@ -197,10 +197,10 @@ int a2a_status_clear(a2a_ctx* ctx);
 
 /* In-kernel trace.  While enabled, thread 0 of every block stamps the SM cycle counter
  * at each phase boundary of the launches that follow (slot 0 of a block holds the
- * nanosecond global timer at its start; then start, routed, sent, send-arrived,
- * dispatch-seen, expert-done, expert-arrived, combine-done).  a2a_trace_read
- * synchronises the device and copies the stamps of the most recent traced launch to
- * host memory: `out` must hold max_blocks * 16 int64.  Both calls synchronise: keep them
+ * nanosecond global timer at its start; then start, routed, sent, dispatch-seen,
+ * expert-done, expert-seen, combine-done).  a2a_trace_read synchronises the device and copies the
+ * stamps of the most recent traced launch to host memory: `out` must hold
+ * max_blocks * 8 int64.  Both calls synchronise: keep them
  * off the timed path.  Replaces the profile buffer of the final reference submission
  * (submission_v9.py:117, :162-184, p2p_state_get_profile). */
 int a2a_trace_enable(a2a_ctx* ctx, int on);
