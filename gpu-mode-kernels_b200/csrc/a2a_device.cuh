@@ -13,13 +13,18 @@
 //     its own GPU a gpu-scope release of a local word, for the peers one fence.sys and then
 //     relaxed system-scope stores of this call's epoch into one flag word per peer;
 //   * on the consumer GPU one "watcher" thread per flag polls it with relaxed system-scope
-//     loads (an acquire load per poll would run a fence per iteration), fences once at
-//     system scope when it has seen the epoch, and re-publishes it in a local word with a
-//     gpu-scope release; everybody else waits on the local word at gpu scope.
+//     loads (strong, L1-bypassing; an acquire load per poll would run a fence per
+//     iteration) and re-publishes it in a local word with a gpu-scope fence + release;
+//     everybody else waits on the local word at gpu scope.  The consumer side deliberately
+//     has no system-scope fence: with peers mapped, a fence.sys is a flush round trip over
+//     NVLink that queues behind the row traffic (5-15 us when measured), and it protects
+//     nothing here -- the producer's fence.sys completed only after its rows were performed
+//     in OUR L2, and every later read of those rows bypasses L1.  This is the discipline
+//     NCCL's primitives use as well (system fence on the posting side only).
 // The PTX memory model makes causality order transitive across edges of different scope,
 // so a row stored by any block of GPU A is visible to any block of GPU B that has seen
-// B's local word, with 2*world system fences per GPU and call instead of thousands (none
-// at all on a single GPU).
+// B's local word, with two system fences per GPU and call instead of thousands (none at
+// all on a single GPU).
 // Flags carry a monotonically increasing call number ("epoch"), are never reset, and
 // every (source, destination) pair has its own flag word on its own 128-byte line.
 // Every wait is bounded by a wall-clock budget; on expiry the kernel records
@@ -201,9 +206,9 @@ __device__ __forceinline__ bool wait_epoch(Load load, Acquire acquire, uint32_t 
     }
 }
 
-// A flag another GPU writes: system scope.
+// A flag another GPU writes: polled with strong system-scope loads; gpu-scope fence on success.
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
-    return wait_epoch([flag] { return ld_relaxed_sys(flag); }, [] { fence_acq_rel_sys(); }, epoch, p, phase, peer);
+    return wait_epoch([flag] { return ld_relaxed_sys(flag); }, [] { fence_acq_rel_gpu(); }, epoch, p, phase, peer);
 }
 
 // A word a thread of this GPU writes: gpu scope.

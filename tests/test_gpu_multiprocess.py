@@ -25,19 +25,27 @@ def _worker(rank, ws, port, cases, q):
     ok, msg = True, ""
     try:
         for (E, K, H, T, seed, iters, payload) in cases:
-            datas = [pkg.generate_input(E, K, H, T, seed=seed, rank=r, world_size=ws, ragged=True) for r in range(ws)]
-            cfg = datas[0][0]
-            rds_cpu = [d[1] for d in datas]
-            _, ys = O.simulate(cfg, ws, rds_cpu)
-            mine = datas[rank][1].to(f"cuda:{rank}")
-            y = None
-            for _ in range(iters):  # back-to-back, no host sync: epochs and slab reuse under real concurrency
-                y = custom_kernel((cfg, mine, rank, ws), payload=payload)
+            # two different input sets, alternated: a flag that overtook its data would hand a
+            # consumer the other set's rows, which the comparison catches
+            sets = []
+            for sd in (seed, seed + 1000):
+                datas = [pkg.generate_input(E, K, H, T, seed=sd, rank=r, world_size=ws, ragged=True) for r in range(ws)]
+                cfg = datas[0][0]
+                rds_cpu = [d[1] for d in datas]
+                _, ys = O.simulate(cfg, ws, rds_cpu)
+                sets.append((rds_cpu, ys, datas[rank][1].to(f"cuda:{rank}")))
+            outs = []
+            for i in range(iters):  # back-to-back, no host sync: epochs and slab reuse under real concurrency
+                outs.append(custom_kernel((cfg, sets[i % 2][2], rank, ws), payload=payload))
             torch.cuda.synchronize()
             for ctx in _CONTEXTS.values():
                 ctx.check()
             try:
-                check_y(cfg, ws, rds_cpu, {rank: y}, ys, payload, ranks=[rank])
+                for i in (0, 1, iters - 2, iters - 1):
+                    rds_cpu, ys, _ = sets[i % 2]
+                    check_y(cfg, ws, rds_cpu, {rank: outs[i]}, ys, payload, ranks=[rank])
+                for i in range(2, iters):
+                    assert torch.equal(outs[i].view(torch.int16), outs[i - 2].view(torch.int16)), f"iteration {i} differs"
             except AssertionError as e:  # noqa: PERF203
                 ok, msg = False, f"case {(E, K, H, T, payload)}: {e}"
                 break
