@@ -190,6 +190,21 @@ int a2a_route_buffers(a2a_ctx* ctx, int32_t** slots, int32_t** send_counts);
  * ([num_tokens*K] and [num_experts] int32) on `stream`. */
 int a2a_copy_route(a2a_ctx* ctx, int32_t* slots_out, int32_t* send_counts_out, void* stream);
 
+/* Routing tables without any allocation, for callers that cannot call cudaMalloc where
+ * they need them (hosts whose memory pool owns the device, plugins barred from the
+ * allocator after start-up, loops that cannot afford a synchronising allocation).  It has
+ * no counterpart in the reference, whose state is always allocated up front.  Needs no
+ * context; runs on the CURRENT device; writes slots_out [num_tokens * experts_per_token]
+ * and send_counts_out [num_experts] (device memory of the caller) with the same values
+ * a2a_route + a2a_copy_route give.  Its working tables are a 1 MiB static device array
+ * held by every GPU that loads the library.  Limits: num_experts <= 1024, num_tokens <=
+ * 4096, experts_per_token <= 32 -- larger requests return A2A_ERR_CONFIG and enqueue
+ * nothing.  The first call on a device resolves the array's device address: make it
+ * before any stream capture.  All calls on a device share the array (the kernel clears
+ * what it uses); calls whose kernels overlap on the GPU race -- keep them ordered. */
+int a2a_route_noalloc(const int32_t* topk_idx, int num_tokens, int num_experts, int experts_per_token,
+                      int32_t* slots_out, int32_t* send_counts_out, void* stream);
+
 /* Read (and optionally clear) the first error recorded by a kernel.  Waits for
  * nothing: reads what is there now. */
 int a2a_status(a2a_ctx* ctx, a2a_status_t* out);
