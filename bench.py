@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--workload", default="c4")
     ap.add_argument("--payload", default=None, help="direct | dedup | fp8 (default: the workload's own)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--verify", action="store_true",
+                    help="after timing, check one forward of every rank against the CPU checker (rank 0 computes it)")
     ap.add_argument("--per-phase-launches", action="store_true",
                     help="run the forward as one kernel per phase instead of one cooperative launch")
     return ap.parse_args()
@@ -387,6 +389,32 @@ def main():
                                   f"threads; dispatch+combine of the reference's Python path, best of 3; expert "
                                   f"placeholder on valid rows ({1e3 * min(expert_s):.1f} ms) not counted"}
 
+    verified = None
+    if args.verify:
+        # one more forward; every rank's output goes to rank 0, which alone runs the CPU checker
+        yv = ctx.forward(rd.x, rd.indices, rd.weights)
+        sync_all()
+        ctx.check()
+        gathered = [torch.empty_like(yv) for _ in range(ws)] if rank == 0 else None
+        if ws > 1:
+            dist.gather(yv, gathered, dst=0)
+        else:
+            gathered = [yv]
+        if rank == 0:
+            from oracle import a2a_oracle as O
+
+            rds = [pkg.workload_input(args.workload, r, ws)[1] for r in range(ws)]
+            _, ys = O.simulate(cfg, ws, rds)
+            tol = 6e-2 if payload == "fp8" else 2e-2
+            worst, outliers = 0.0, 0
+            for r in range(ws):
+                d = (gathered[r].cpu().float() - ys[r].float()).abs() / (tol + tol * ys[r].float().abs())
+                worst = max(worst, float(d.max()))
+                outliers += int((d > 1).sum())
+            verified = {"rtol_atol": tol, "worst_diff_over_tol": worst, "elements_outside": outliers,
+                        "ok": bool(worst <= (1.25 if payload == "fp8" else 1.0))}
+        sync_all()
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": ms * 1e3, "unit": "us", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
@@ -401,6 +429,8 @@ def main():
         }
         if nvlink is not None:
             line["nvlink"] = nvlink
+        if verified is not None:
+            line["verified"] = verified
         print(json.dumps(line), flush=True)
 
     sync_all()

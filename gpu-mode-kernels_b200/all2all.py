@@ -12,6 +12,7 @@ All compute is in liba2a.so; nothing here has a CPU or PyTorch fallback.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional, Sequence, Tuple
 
 import torch
@@ -32,10 +33,13 @@ class A2AContext:
     """State of one rank for one (config, process group): buffers, peer mappings, flags."""
 
     def __init__(self, cfg: MoEConfig, rank: int, world_size: int, *, device: Optional[int] = None,
-                 payload: str = "direct", timeout_ms: int = 2000, group=None, connect: bool = True):
+                 payload: str = "direct", timeout_ms: Optional[int] = None, group=None, connect: bool = True):
         if cfg.in_dtype != cfg.out_dtype or cfg.in_dtype not in _DTYPES:
             raise A2AError(_lib.A2A_ERR_CONFIG, f"unsupported dtypes {cfg.in_dtype}/{cfg.out_dtype}")
         self.lib = _lib.load()
+        if timeout_ms is None:
+            # budget of every device-side wait on a peer; ranks must reach a call within it of each other
+            timeout_ms = int(os.environ.get("A2A_TIMEOUT_MS", "5000"))
         self.cfg, self.rank, self.world_size = cfg, rank, world_size
         self.payload = payload
         if device is None:
