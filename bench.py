@@ -217,7 +217,7 @@ def reference_main(args, rank: int, ws: int):
         "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": ws, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.workload, ws, "direct"),
+        "config": workload_config(args.workload, ws, "dedup"),
         "cpu_baseline": {"value": us, "unit": "us", "cores": min(cores, ws * threads), "kind": "port", "sample": sample},
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -267,7 +267,7 @@ def main():
         dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
 
     wl = pkg.WORKLOADS[args.workload]
-    payload = args.payload or wl.get("payload", "direct")
+    payload = args.payload or wl.get("payload", "dedup")
     cfg, rd_cpu, _, _ = pkg.workload_input(args.workload, rank, ws)
     rd = rd_cpu.to(dev)
     T, K, H = rd.num_tokens, cfg.experts_per_token, cfg.hidden_dim
