@@ -34,7 +34,7 @@ Layout make_layout(const a2a_config& c) {
     l.off_meta = off;  // everything from here up to the wire rows starts as zero
     off = align_up(off + L * ws * T * sizeof(int32_t), 256);
     l.off_counts = off;
-    off = align_up(off + ws * L * sizeof(int32_t), 256);
+    off = align_up(off + ws * kMaxChunks * L * sizeof(int32_t), 256);
     l.off_flags = off;
     off = align_up(off + (size_t)kNumFlagKinds * A2A_MAX_WORLD * kFlagStride * sizeof(uint32_t), 256);
     l.stage_row_bytes = 0;
@@ -294,6 +294,20 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     p.stage_row_bytes = c->lay.stage_row_bytes;
     p.rank = cfg->rank; p.ws = cfg->world_size; p.E = E; p.K = K; p.H = H; p.T_max = T; p.L = L;
     p.timeout_ns = (long long)c->cfg.timeout_ms * 1000000LL;
+    {
+        // Token chunks the call is pipelined in (whole 32-token words).  Default 1: measured on
+        // B200 the per-chunk publication (a ticket round and a system fence each) costs more than
+        // the overlap returns -- c4, DEDUP: 32.7 / 37.5 / 59.3 us with 1 / 2 / 4 chunks on one GPU,
+        // 70.7 / 68.1 / 89.3 us on two.  A2A_CHUNKS=2..4 opts in; every rank of a group must agree.
+        const int Wmax = (T + 31) / 32;
+        int chunks = 1;
+        if (const char* env = getenv("A2A_CHUNKS")) {
+            const int v = atoi(env);
+            if (v >= 1 && v <= kMaxChunks) chunks = v < Wmax ? v : Wmax;
+        }
+        p.wpc = (Wmax + chunks - 1) / chunks;
+        p.chunks = (Wmax + p.wpc - 1) / p.wpc;
+    }
     p.slot = reinterpret_cast<int*>(c->scratch + o_slot);
     p.send_counts = reinterpret_cast<int*>(c->scratch + o_send);
     p.tickets = reinterpret_cast<uint32_t*>(c->scratch + o_tick);

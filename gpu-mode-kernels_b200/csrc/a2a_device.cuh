@@ -44,6 +44,7 @@ namespace a2a {
 constexpr int kThreads = 256;    // every kernel of the path runs 256-thread blocks
 constexpr int kFlagStride = 32;  // uint32 words between two flags = 128 bytes
 constexpr int kFp8Block = 128;   // elements sharing one fp32 scale
+constexpr int kMaxChunks = 4;    // token chunks a call is pipelined in (whole 32-token bitmap words each)
 enum FlagKind : int { kFlagDispatch = 0, kFlagExpert = 1, kFlagBarrier = 2, kNumFlagKinds = 3 };
 enum Phase : int { kPhaseRoute = 1, kPhaseSend = 2, kPhaseRecv = 3, kPhaseExpert = 4, kPhaseCombine = 5, kPhaseBarrier = 6 };
 // In-kernel trace: thread 0 of every block stamps these points with the SM cycle counter
@@ -60,18 +61,20 @@ struct DevParams {
     // byte offsets inside a symmetric region (identical on every rank)
     size_t off_rows;        // [L][ws][T_max][H] elements: slab (l, src) holds the rows src sent to local expert l
     size_t off_meta;        // [L][ws][T_max] int32: (token << 8) | k of every row
-    size_t off_counts;      // [ws][L] int32: rows source s sent to local expert l in the current call
+    size_t off_counts;      // [ws][kMaxChunks][L] int32: rows source s sent to local expert l up to the END of chunk c
     size_t off_flags;       // [kNumFlagKinds][A2A_MAX_WORLD][kFlagStride] u32 epochs, written by the peers
     size_t off_stage;       // [ws][T_max][stage_row_bytes]: one wire row per (source, token)   (DEDUP / FP8)
     int stage_row_bytes;
     int rank, ws, E, K, H, T_max, L;
     int T;                  // tokens of this rank in the current call
+    int chunks;             // token chunks per call, 1..kMaxChunks (same on every rank)
+    int wpc;                // 32-token bitmap words per chunk: chunk c = tokens [32*c*wpc, 32*(c+1)*wpc)
     uint32_t epoch;
     long long timeout_ns;
     // local scratch of this rank
     int* slot;              // [T_max*K] slot of pair (t,k) inside slab (expert, this rank), -1 = dropped
     int* send_counts;       // [E]
-    uint32_t* tickets;      // [2] block-arrival counters, one per publishing phase
+    uint32_t* tickets;      // [2][kMaxChunks] block-arrival counters, one per publishing phase and chunk
     uint32_t* seen;         // [2][A2A_MAX_WORLD][kFlagStride] local re-publication of the peers' dispatch / expert flags
     a2a_status_t* status;
     long long* trace;       // [blocks][kNumStamps] or nullptr when tracing is off
@@ -216,6 +219,15 @@ __device__ __forceinline__ bool wait_flag_gpu(const uint32_t* flag, uint32_t epo
     return wait_epoch([flag] { return ld_relaxed_gpu(flag); }, [] { fence_acq_rel_gpu(); }, epoch, p, phase, peer);
 }
 
+// What a flag word carries once chunk c of this call is published: monotonic over calls and chunks.
+__device__ __forceinline__ uint32_t flag_value(const DevParams& p, int c) { return p.epoch * 8u + (uint32_t)c + 1u; }
+
+// First and one-past-last token of chunk c.
+__device__ __forceinline__ int chunk_begin(const DevParams& p, int c) { return min(p.T, 32 * c * p.wpc); }
+__device__ __forceinline__ int chunk_end(const DevParams& p, int c) {
+    return c == p.chunks - 1 ? p.T : min(p.T, 32 * (c + 1) * p.wpc);
+}
+
 __device__ __forceinline__ uint32_t* seen_ptr(const DevParams& p, int kind, int index) {
     return p.seen + ((size_t)kind * A2A_MAX_WORLD + index) * kFlagStride;
 }
@@ -223,9 +235,9 @@ __device__ __forceinline__ uint32_t* seen_ptr(const DevParams& p, int kind, int 
 // Watcher duty: wait for peer `index`'s flag of `kind` at system scope, then hand it to
 // the rest of this GPU through the local word.  On a timeout nothing is handed on and
 // the local waiters run into the recorded timeout.
-__device__ __forceinline__ bool watch_and_republish(const DevParams& p, int kind, int index, int phase) {
-    const bool ok = wait_flag_sys(flag_ptr(p.peer[p.rank], p.off_flags, kind, index), p.epoch, p, phase, index);
-    if (ok) st_release_gpu(seen_ptr(p, kind, index), p.epoch);
+__device__ __forceinline__ bool watch_and_republish(const DevParams& p, int kind, int index, int phase, uint32_t value) {
+    const bool ok = wait_flag_sys(flag_ptr(p.peer[p.rank], p.off_flags, kind, index), value, p, phase, index);
+    if (ok) st_release_gpu(seen_ptr(p, kind, index), value);
     return ok;
 }
 

@@ -16,6 +16,7 @@ namespace a2a {
 //   wpre [Wc][E]  number of set bits in the words before w (exclusive scan over w)
 //   cnt  [E]      tokens using expert e = rows this rank sends to e
 //   pre  [max(E+2, Wmax+1)] scratch of the receive side: slab prefix sums or the token mask
+//   base [E]      receive side: first slot of the current chunk in every slab of a source
 //   idx  [T*K]    this rank's top-k expert indices (one coalesced pass over global memory;
 //                 every later look-up, including the repeat check, is a shared-memory read)
 // Wc = ceil(T/32) words of the current call; the allocation is sized for T_max.
@@ -25,6 +26,7 @@ struct BlockSmem {
     int* wpre;
     int* cnt;
     int* pre;
+    int* base;
     int* idx;
 };
 
@@ -35,7 +37,7 @@ __host__ __device__ inline size_t pre_ints(int E, int T_max) {
 
 __host__ __device__ inline size_t block_smem_ints(int E, int T_max, int K) {
     const size_t W = (size_t)(T_max + 31) / 32;
-    return 2 * W * E + E + pre_ints(E, T_max) + (size_t)T_max * K;
+    return 2 * W * E + E + pre_ints(E, T_max) + E + (size_t)T_max * K;
 }
 
 __device__ __forceinline__ BlockSmem carve_smem(int* base, int E, int T_max) {
@@ -45,7 +47,8 @@ __device__ __forceinline__ BlockSmem carve_smem(int* base, int E, int T_max) {
     s.wpre = base + W * E;
     s.cnt = base + 2 * W * E;
     s.pre = s.cnt + E;
-    s.idx = s.pre + pre_ints(E, T_max);
+    s.base = s.pre + pre_ints(E, T_max);
+    s.idx = s.base + E;
     return s;
 }
 
@@ -108,29 +111,41 @@ __device__ __forceinline__ int pair_slot(const DevParams& p, const BlockSmem& s,
     return s.wpre[w * p.E + e] + __popc(s.bits[w * p.E + e] & ((1u << (t & 31)) - 1u));
 }
 
-// Publication of a phase by all threads of the block that arrived last.  Our own rank
-// is served first and at gpu scope (its consumers are blocks of this GPU); the peers
-// get ONE system fence, then this call's epoch in their flag word of `kind`.
-__device__ __forceinline__ void publish_flags(const DevParams& p, int kind) {
+// Publication of one chunk of a phase by all threads of the block that arrived last.  Our
+// own rank is served first and at gpu scope (its consumers are blocks of this GPU); the
+// peers get ONE system fence, then the chunk's flag value in their flag word of `kind`.
+__device__ __forceinline__ void publish_flags(const DevParams& p, int kind, uint32_t value) {
     const int tid = threadIdx.x;
     __syncthreads();  // whatever the block wrote for this publication has been issued
-    if (tid == 0) st_release_gpu(seen_ptr(p, kind, p.rank), p.epoch);  // fence.gpu + store
+    if (tid == 0) st_release_gpu(seen_ptr(p, kind, p.rank), value);  // fence.gpu + store
     if (p.ws > 1) {
         if (tid == 0) __threadfence_system();  // orders every block's rows (seen through the tickets) for the peers
         __syncthreads();
-        if (tid < p.ws && tid != p.rank) st_relaxed_sys(flag_ptr(p.peer[tid], p.off_flags, kind, p.rank), p.epoch);
+        if (tid < p.ws && tid != p.rank) st_relaxed_sys(flag_ptr(p.peer[tid], p.off_flags, kind, p.rank), value);
     }
 }
 
-// Dispatch publication: per destination the row count of every (this source, local
-// expert) slab, then the flags.
-__device__ __forceinline__ void publish_dispatch(const DevParams& p, const BlockSmem& s) {
-    for (int e = threadIdx.x; e < p.E; e += kThreads) {
-        const int d = e / p.L, l = e - d * p.L;
-        reinterpret_cast<int*>(p.peer[d] + p.off_counts)[p.rank * p.L + l] = s.cnt[e];
-        p.send_counts[e] = s.cnt[e];
+// Rows this rank sends to expert e from the tokens before the end of chunk c.
+__device__ __forceinline__ int sent_up_to_chunk(const DevParams& p, const BlockSmem& s, int c, int e) {
+    const int Wc = (p.T + 31) >> 5;
+    const int wb = (c + 1) * p.wpc;
+    return (c == p.chunks - 1 || wb >= Wc) ? s.cnt[e] : s.wpre[wb * p.E + e];
+}
+
+// Dispatch publication of chunk c.  Routing is known before any row moves, so the first
+// chunk carries the cumulative row counts of EVERY chunk for every (this source, local
+// expert) slab; later chunks only raise the flag.
+__device__ __forceinline__ void publish_dispatch(const DevParams& p, const BlockSmem& s, int c) {
+    if (c == 0) {
+        for (int i = threadIdx.x; i < p.E * p.chunks; i += kThreads) {
+            const int cc = i / p.E, e = i - cc * p.E;
+            const int d = e / p.L, l = e - d * p.L;
+            reinterpret_cast<int*>(p.peer[d] + p.off_counts)[((size_t)p.rank * kMaxChunks + cc) * p.L + l] =
+                sent_up_to_chunk(p, s, cc, e);
+        }
+        for (int e = threadIdx.x; e < p.E; e += kThreads) p.send_counts[e] = s.cnt[e];
     }
-    publish_flags(p, kFlagDispatch);
+    publish_flags(p, kFlagDispatch, flag_value(p, c));
 }
 
 // Copy one row of nvec 16-byte vectors with all 256 threads, up to four loads in flight each.
@@ -159,18 +174,15 @@ __device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* _
 //   once per destination into stage[src][t] (FP8: quantised on the fly, one fp32
 //   scale per 128 values); every slab row that wants it gets its (token, k) word,
 //   through which the receiver finds the wire row when it fans out.
-// The block that finishes last publishes counts and flags.
+// Work is done chunk of tokens by chunk; the block that finishes a chunk last publishes it.
 // ---------------------------------------------------------------------------
 template <typename T, int PAYLOAD>
-__device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& s) {
+__device__ __forceinline__ void send_chunk(const DevParams& p, const BlockSmem& s, int c) {
     const int tid = threadIdx.x;
     const int K = p.K, nvec = p.H >> 3;
-    stamp(p, kStampStart);
-    route_build(p, s);
-    stamp(p, kStampRouted);
+    const int ta = chunk_begin(p, c), tb = chunk_end(p, c);  // this chunk's tokens
     if (PAYLOAD == A2A_PAYLOAD_DIRECT) {
-        const int P = p.T * K;
-        for (int pair = blockIdx.x; pair < P; pair += gridDim.x) {
+        for (int pair = ta * K + (int)blockIdx.x; pair < tb * K; pair += gridDim.x) {
             const int t = pair / K, k = pair - t * K;
             const int e = s.idx[pair];
             const int j = pair_slot(p, s, t, k, e);
@@ -183,8 +195,7 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
             if (tid == 0) reinterpret_cast<int*>(p.peer[d] + p.off_meta)[row] = (t << 8) | k;
         }
     } else {
-        const int items = p.T * p.ws;
-        for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        for (int it = ta * p.ws + (int)blockIdx.x; it < tb * p.ws; it += gridDim.x) {
             const int t = it / p.ws, d = it - t * p.ws;
             // which of the token's experts live on d: each of them gets its slab row's (token, k)
             // word there; the row itself crosses the wire once
@@ -232,8 +243,17 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
             }
         }
     }
+    if (grid_arrive_last(p.tickets + kTicketSend * kMaxChunks + c)) publish_dispatch(p, s, c);
+}
+
+// The sending half as its own kernel: routing, then every chunk in order.
+template <typename T, int PAYLOAD>
+__device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& s) {
+    stamp(p, kStampStart);
+    route_build(p, s);
+    stamp(p, kStampRouted);
+    for (int c = 0; c < p.chunks; ++c) send_chunk<T, PAYLOAD>(p, s, c);
     stamp(p, kStampSent);
-    if (grid_arrive_last(p.tickets + kTicketSend)) publish_dispatch(p, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -255,19 +275,23 @@ __device__ __forceinline__ void send_phase(const DevParams& p, const BlockSmem& 
 //   SCALE: the placeholder expert op, T(float(row) * (1 + rank)), on the way.
 // Without FANOUT the row is read from the slab itself (in place).
 template <typename T, int PAYLOAD, bool FANOUT, bool SCALE>
-__device__ __forceinline__ void rows_of_source(const DevParams& p, int* pre, int s, int part, int nparts) {
+__device__ __forceinline__ void rows_of_source(const DevParams& p, int* pre, int* base, int s, int c, int part,
+                                               int nparts) {
     constexpr bool from_wire = FANOUT && PAYLOAD != A2A_PAYLOAD_DIRECT;
     constexpr bool fp8 = from_wire && PAYLOAD == A2A_PAYLOAD_FP8;
     const int tid = threadIdx.x;
     uint8_t* self = p.peer[p.rank];
-    const int* counts = reinterpret_cast<const int*>(self + p.off_counts) + (size_t)s * p.L;
+    // rows of chunk c in slab (l, s): slots [counts up to chunk c-1, counts up to chunk c)
+    const int* counts = reinterpret_cast<const int*>(self + p.off_counts) + ((size_t)s * kMaxChunks + c) * p.L;
     for (int l = tid; l < p.L; l += kThreads) {
-        int c = ld_stream(counts + l);
-        if (c < 0 || c > p.T_max) {
-            record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, c);
-            c = 0;
+        int hi = ld_stream(counts + l);
+        int lo = c > 0 ? ld_stream(counts - p.L + l) : 0;
+        if (lo < 0 || hi < lo || hi > p.T_max) {
+            record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, hi);
+            lo = hi = 0;
         }
-        pre[l] = c;
+        pre[l] = hi - lo;
+        base[l] = lo;
     }
     block_exclusive_scan(pre, p.L);
     const int total = pre[p.L];
@@ -277,7 +301,7 @@ __device__ __forceinline__ void rows_of_source(const DevParams& p, int* pre, int
     const int* meta = reinterpret_cast<const int*>(self + p.off_meta);
     for (int r = part; r < total; r += nparts) {
         const int l = upper_slab(pre, p.L, r);
-        const int j = r - pre[l];
+        const int j = base[l] + r - pre[l];
         const size_t ri = ((size_t)l * p.ws + s) * p.T_max + j;
         uint4* row = rows + ri * nvec;
         const uint8_t* wire = nullptr;
@@ -319,9 +343,10 @@ __device__ __forceinline__ void rows_of_source(const DevParams& p, int* pre, int
 }
 
 template <typename T, int PAYLOAD, bool WAIT, bool FANOUT, bool SCALE, bool PUBLISH>
-__device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem& sm) {
+__device__ __forceinline__ void expert_chunk(const DevParams& p, const BlockSmem& sm, int c) {
     __shared__ int s_seen;
     const int tid = threadIdx.x;
+    const uint32_t want = flag_value(p, c);
     // block b serves source b % ws together with the other blocks of that residue;
     // a grid smaller than the world size lets each block walk several sources alone
     const bool many = (int)gridDim.x >= p.ws;
@@ -335,27 +360,34 @@ __device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem
             // for our own rank (whose publisher writes the local word itself), wait locally
             if (tid == 0)
                 s_seen = (part == 0 && s != p.rank
-                              ? watch_and_republish(p, kFlagDispatch, s, kPhaseRecv)
-                              : wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), p.epoch, p, kPhaseRecv, s)) ? 1 : 0;
+                              ? watch_and_republish(p, kFlagDispatch, s, kPhaseRecv, want)
+                              : wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s)) ? 1 : 0;
             __syncthreads();
             const int seen = s_seen;
             __syncthreads();
             if (!seen) break;  // timeout recorded; the rows of this source are left alone
-            stamp(p, kStampDispatchSeen);
+            if (c == 0) stamp(p, kStampDispatchSeen);
         }
         constexpr bool staged = (PAYLOAD != A2A_PAYLOAD_DIRECT);
-        if ((staged && FANOUT) || SCALE) rows_of_source<T, PAYLOAD, FANOUT, SCALE>(p, sm.pre, s, part, nparts);
-        __syncthreads();  // sm.pre is reused by the next source
+        if ((staged && FANOUT) || SCALE)
+            rows_of_source<T, PAYLOAD, FANOUT, SCALE>(p, sm.pre, sm.base, s, c, part, nparts);
+        __syncthreads();  // sm.pre / sm.base are reused by the next source
     }
-    stamp(p, kStampExpertDone);
     if (PUBLISH) {
-        if (grid_arrive_last(p.tickets + kTicketExpert)) {
+        if (grid_arrive_last(p.tickets + kTicketExpert * kMaxChunks + c)) {
             // after a timeout the outputs are incomplete: say nothing, the home ranks run into their own budget
             if (tid == 0) s_seen = (ld_volatile_i32(&p.status->code) != A2A_ERR_TIMEOUT) ? 1 : 0;
             __syncthreads();
-            if (s_seen) publish_flags(p, kFlagExpert);
+            if (s_seen) publish_flags(p, kFlagExpert, want);
         }
     }
+}
+
+// The receive side as its own kernel: every chunk in order.
+template <typename T, int PAYLOAD, bool WAIT, bool FANOUT, bool SCALE, bool PUBLISH>
+__device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem& sm) {
+    for (int c = 0; c < p.chunks; ++c) expert_chunk<T, PAYLOAD, WAIT, FANOUT, SCALE, PUBLISH>(p, sm, c);
+    stamp(p, kStampExpertDone);
 }
 
 // ---------------------------------------------------------------------------
@@ -374,12 +406,16 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
     const int nwarps = (int)gridDim.x * (kThreads / 32);
     const int K = p.K, nvec = p.H >> 3;
     const int nseg = (nvec + 31) >> 5;
-    const int items = p.T * nseg;
-    if (warp < p.ws && warp != p.rank && lane == 0) watch_and_republish(p, kFlagExpert, warp, kPhaseCombine);
+    for (int c = 0; c < p.chunks; ++c) {
+    const uint32_t want = flag_value(p, c);
+    const int ta = chunk_begin(p, c), tb = chunk_end(p, c);
+    const int items = (tb - ta) * nseg;
+    // warp d of the grid watches rank d's flag for this chunk before its own items
+    if (warp < p.ws && warp != p.rank && lane == 0) watch_and_republish(p, kFlagExpert, warp, kPhaseCombine, want);
     __syncwarp();
-    unsigned ready = 0u;  // ranks this lane has already seen ready
+    unsigned ready = 0u;  // ranks this lane has already seen ready for this chunk
     for (int item = warp; item < items; item += nwarps) {
-        const int t = item / nseg, seg = item - t * nseg;
+        const int t = ta + item / nseg, seg = item % nseg;
         const int v = seg * 32 + lane;
         unsigned long long my_row = 0ull;
         float my_w = 0.f;
@@ -395,13 +431,13 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
                     reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
                     (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec);
                 if (!((ready >> d) & 1u)) {
-                    ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), p.epoch, p, kPhaseCombine, d);
+                    ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), want, p, kPhaseCombine, d);
                     ready |= 1u << d;
                 }
             }
         }
         if (!__all_sync(0xffffffffu, ok)) return;  // timeout recorded; leave the remaining output untouched
-        if (item == warp) stamp(p, kStampExpertSeen);
+        if (item == warp && c == 0) stamp(p, kStampExpertSeen);
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -428,6 +464,7 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
         }
         if (v < nvec) st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v, pack8<T>(acc));
     }
+    }  // chunks
     __syncthreads();
     stamp(p, kStampCombineDone);
 }
@@ -466,13 +503,25 @@ __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant
 }
 
 // The whole path in one launch.  Launched cooperatively so that every block is
-// resident: a block that has finished sending waits (bounded) on words that the
-// last-finishing block of this very grid, or a peer GPU, will set.
+// resident: a block waits (bounded) on words that the last-finishing block of this very
+// grid, or a peer GPU, will set.  The call is pipelined in token chunks: a block sends
+// chunk c, then does its share of the expert work of chunk c-1 (whose rows had a whole
+// chunk of sending time to land), so the phase boundaries of all but the last chunk hide
+// behind NVLink-bound sending; the combine then walks the chunks in the same order.
+// Publishing a chunk never depends on any receive-side work, so there is no wait cycle.
 template <typename T, int PAYLOAD>
 __global__ void __launch_bounds__(kThreads) forward_kernel(const __grid_constant__ DevParams p) {
     const BlockSmem s = carve_smem(a2a_dyn_smem, p.E, p.T_max);
-    send_phase<T, PAYLOAD>(p, s);
-    expert_phase<T, PAYLOAD, true, true, true, true>(p, s);
+    stamp(p, kStampStart);
+    route_build(p, s);
+    stamp(p, kStampRouted);
+    for (int c = 0; c < p.chunks; ++c) {
+        send_chunk<T, PAYLOAD>(p, s, c);
+        if (c >= 1) expert_chunk<T, PAYLOAD, true, true, true, true>(p, s, c - 1);
+    }
+    stamp(p, kStampSent);
+    expert_chunk<T, PAYLOAD, true, true, true, true>(p, s, p.chunks - 1);
+    stamp(p, kStampExpertDone);
     combine_phase<T>(p);
 }
 
@@ -489,7 +538,7 @@ __global__ void __launch_bounds__(kThreads) export_dispatch_kernel(const __grid_
     const int* counts = reinterpret_cast<const int*>(self + p.off_counts);
     for (int i = tid; i < nslab; i += kThreads) {
         const int l = i / p.ws, s = i - l * p.ws;
-        const int c = counts[s * p.L + l];
+        const int c = counts[((size_t)s * kMaxChunks + p.chunks - 1) * p.L + l];
         prefix[i] = (c < 0 || c > p.T_max) ? 0 : c;
     }
     block_exclusive_scan(prefix, nslab);

@@ -335,3 +335,40 @@ def test_forward_one_launch_equals_per_phase_launches(payload, fused):
             world.close()
     finally:
         ctx.close()
+
+
+@pytest.mark.parametrize("chunks", [2, 4])
+@pytest.mark.parametrize("payload", PAYLOADS)
+def test_token_chunk_pipelining_gives_the_same_results(chunks, payload, monkeypatch):
+    """A2A_CHUNKS > 1 pipelines a call in token chunks (per-chunk counts, flags and tickets);
+    dispatch stays bit-exact and combine within tolerance, ragged token counts included."""
+    monkeypatch.setenv("A2A_CHUNKS", str(chunks))
+    ws = 4
+    datas = [pkg.generate_input(32, 4, 512, 200, seed=21, rank=r, world_size=ws, ragged=True) for r in range(ws)]
+    cfg = datas[0][0]
+    rds_cpu = [d[1] for d in datas]
+    disp, ys = O.simulate(cfg, ws, rds_cpu)
+    world = LocalWorld(cfg, ws, payload=payload)
+    try:
+        rds = [rd.to(DEV) for rd in rds_cpu]
+        world.dispatch(rds)
+        check_dispatch(world, [(d.expert_num_tokens, d.rows, d.meta) for d in disp], payload)
+        for fwd in (world.forward_phases, world.forward):
+            out = fwd(rds)
+            torch.cuda.synchronize()
+            world.check()
+            check_y(cfg, ws, rds_cpu, out, ys, payload)
+    finally:
+        world.close()
+    # the one-launch kernel interleaves sending chunk c with the expert work of chunk c-1
+    cfg1, rd1, _, _ = pkg.generate_input(32, 4, 512, 200, seed=22, rank=0, world_size=1)
+    _, y1 = O.simulate(cfg1, 1, [rd1])
+    ctx = A2AContext(cfg1, 0, 1, device=0, payload=payload)
+    try:
+        d = rd1.to(DEV)
+        y = ctx.forward(d.x, d.indices, d.weights)
+        torch.cuda.synchronize()
+        ctx.check()
+        check_y(cfg1, 1, [rd1], [y], y1, payload)
+    finally:
+        ctx.close()
