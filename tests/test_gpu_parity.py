@@ -372,3 +372,29 @@ def test_token_chunk_pipelining_gives_the_same_results(chunks, payload, monkeypa
         check_y(cfg1, 1, [rd1], [y], y1, payload)
     finally:
         ctx.close()
+
+
+@pytest.mark.parametrize("spec", pkg.REFERENCE_TESTS + pkg.REFERENCE_BENCHMARKS,
+                         ids=lambda s: "E{}_K{}_H{}_T{}".format(*s[:4]))
+def test_reference_task_shapes_fp16(spec):
+    """The reference task's own nine test and five benchmark shapes (task.yml:48-65) in its own
+    style -- world size 8, fp16, uniform weights, random token count per rank -- held to its own
+    tolerance rtol=1e-2, atol=5e-3 (reference.py:279); dispatch bit-exact."""
+    ws = 8
+    datas = [pkg.reference_task_input(spec, r, ws) for r in range(ws)]
+    cfg = datas[0][0]
+    rds_cpu = [d[1] for d in datas]
+    disp, ys = O.simulate(cfg, ws, rds_cpu)
+    world = LocalWorld(cfg, ws, payload="dedup")
+    try:
+        rds = [rd.to(DEV) for rd in rds_cpu]
+        world.dispatch(rds)
+        check_dispatch(world, [(d.expert_num_tokens, d.rows, d.meta) for d in disp], "dedup")
+        out = world.forward(rds)
+        torch.cuda.synchronize()
+        world.check()
+        for r in range(ws):
+            assert out[r].shape == (rds_cpu[r].num_tokens, cfg.hidden_dim) and out[r].dtype == torch.float16
+            torch.testing.assert_close(out[r].cpu().float(), ys[r].float(), rtol=1e-2, atol=5e-3)
+    finally:
+        world.close()
