@@ -142,10 +142,12 @@ def _ref_rank(rank, ws, port, workload, steps, warmup, threads, q):
     import gpu_mode_kernels_b200 as pkg
     from oracle import a2a_oracle as O
 
-    os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(port)
+    # a private TCP rendezvous: under torchrun the inherited TORCHELASTIC_* variables would make an
+    # env:// rendezvous look for the launcher's store instead of starting ours
+    for k in [k for k in os.environ if k.startswith("TORCHELASTIC_")]:
+        os.environ.pop(k)
     torch.set_num_threads(threads)
-    dist.init_process_group("gloo", rank=rank, world_size=ws)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=ws)
     cfg, rd, _, _ = pkg.workload_input(workload, rank, ws)
     ata = O.PortAllToAll(cfg, rank, ws)
     full_tokens = rd.num_tokens

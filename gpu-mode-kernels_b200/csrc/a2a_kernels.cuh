@@ -15,7 +15,7 @@ namespace a2a {
 //   bits [Wc][E]  bit t%32 of word t/32 set iff token t of this rank uses expert e
 //   wpre [Wc][E]  number of set bits in the words before w (exclusive scan over w)
 //   cnt  [E]      tokens using expert e = rows this rank sends to e
-//   pre  [max(E+2, Wmax+1)] scratch of the receive side: slab prefix sums or the token mask
+//   pre  [E+2]    receive side: prefix sums over the slabs of a source
 //   base [E]      receive side: first slot of the current chunk in every slab of a source
 //   idx  [T*K]    this rank's top-k expert indices (one coalesced pass over global memory;
 //                 every later look-up, including the repeat check, is a shared-memory read)
@@ -30,10 +30,7 @@ struct BlockSmem {
     int* idx;
 };
 
-__host__ __device__ inline size_t pre_ints(int E, int T_max) {
-    const size_t W = (size_t)(T_max + 31) / 32;
-    return (size_t)E + 2 > W + 1 ? (size_t)E + 2 : W + 1;
-}
+__host__ __device__ inline size_t pre_ints(int E, int /*T_max*/) { return (size_t)E + 2; }
 
 __host__ __device__ inline size_t block_smem_ints(int E, int T_max, int K) {
     const size_t W = (size_t)(T_max + 31) / 32;

@@ -178,8 +178,10 @@ int a2a_barrier(a2a_ctx* ctx, void* stream);
 int a2a_export_dispatch(a2a_ctx* ctx, int32_t* counts, void* rows, int32_t* meta, void* stream);
 
 /* Device pointers into this rank's own state (valid until a2a_destroy):
- * the slab rows [L][world][max_num_tokens][H] and counts [world][L]; the layout
- * contract a real expert kernel would consume. */
+ * the slab rows [L][world][max_num_tokens][H] and the row counts [world][4][L] --
+ * cumulative over the (up to 4) token chunks of a call, so with the default single chunk
+ * counts[s][0][l] is the number of valid rows of slab (l, s); the layout contract a real
+ * expert kernel would consume. */
 int a2a_expert_buffers(a2a_ctx* ctx, void** rows, int32_t** counts_by_source);
 
 /* Per-(token,k) slot table [num_tokens*K] int32 and per-expert send counts
