@@ -1,9 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself.
 
-Run in a container that has the reference checkout (default
-``/root/reference``; override with ``A2A_REFERENCE_DIR``):
+Run where the reference checkout is available, pointing ``A2A_REFERENCE_DIR`` at it:
 
-    python tests/golden/make_golden.py
+    A2A_REFERENCE_DIR=/path/to/gpu-mode-kernels python tests/golden/make_golden.py
 
 For every case below it starts ``world_size`` CPU processes on the gloo
 backend, imports the unmodified ``reference.py`` of
@@ -25,7 +24,9 @@ import torch.multiprocessing as mp
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF_DIR = os.path.join(os.environ.get("A2A_REFERENCE_DIR", "/root/reference"), "amd-distributed", "all2all")
+if "A2A_REFERENCE_DIR" not in os.environ:
+    sys.exit("set A2A_REFERENCE_DIR to the checkout of gau-nernst/gpu-mode-kernels")
+REF_DIR = os.path.join(os.environ["A2A_REFERENCE_DIR"], "amd-distributed", "all2all")
 
 # name -> (world_size, generate_input kwargs)
 CASES = {

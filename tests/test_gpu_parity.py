@@ -1,7 +1,7 @@
 """GPU parity: the CUDA path (through the C ABI) against the CPU checker and the golden vectors.
 
 World sizes above one are stepped phase by phase on a single GPU (LocalWorld); the
-real multi-process / multi-GPU path is in test_gpu_multiprocess.py.
+real multi-process / multi-GPU path is in test_x_gpu_multiprocess.py.
 """
 import pytest
 import torch
