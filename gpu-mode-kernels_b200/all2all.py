@@ -162,6 +162,16 @@ class A2AContext:
         _lib.check(self.lib.a2a_export_dispatch(self._h, _ptr(counts), _ptr(rows), _ptr(meta), self._stream()))
         return counts, rows, meta
 
+    def expert_buffers(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Views (no copy) of this rank's slab rows [L, world, T_max, H] and of the cumulative row counts
+        [world, 4, L] -- what a real expert kernel reads and overwrites in place between
+        ``dispatch_recv`` and ``expert_done``."""
+        rows, counts = C.c_void_p(), C.c_void_p()
+        _lib.check(self.lib.a2a_expert_buffers(self._h, C.byref(rows), C.byref(counts)))
+        L, ws, T, H = self.num_local_experts, self.world_size, self.cfg.max_num_tokens, self.cfg.hidden_dim
+        return (_device_view(rows.value, (L, ws, T, H), self.cfg.in_dtype, self.device_index),
+                _device_view(counts.value, (ws, 4, L), torch.int32, self.device_index))
+
     def route_tables(self) -> Tuple[torch.Tensor, torch.Tensor]:
         """Copies of the slot table [num_tokens, K] and per-expert send counts [E] of the last route."""
         n, K, E = self._num_tokens, self.cfg.experts_per_token, self.cfg.num_experts
@@ -216,6 +226,22 @@ class A2AContext:
             self.close()
         except Exception:
             pass
+
+
+class _RawDeviceMemory:
+    """Just enough of the CUDA array interface for torch to wrap library-owned device memory."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _device_view(ptr: int, shape, dtype: torch.dtype, device_index: int) -> torch.Tensor:
+    n = 1
+    for d in shape:
+        n *= d
+    raw = torch.as_tensor(_RawDeviceMemory(ptr, n * torch.empty((), dtype=dtype).element_size()),
+                          device=torch.device("cuda", device_index))
+    return raw.view(dtype).view(*shape)
 
 
 # ---------------------------------------------------------------------------

@@ -240,7 +240,7 @@ def simulate_dispatch(cfg, world_size: int, xs: Sequence[torch.Tensor],
 
 
 def simulate_combine(cfg, world_size: int, disp: Sequence[RankDispatch], weights: Sequence[torch.Tensor],
-                     num_tokens: Sequence[int]) -> List[torch.Tensor]:
+                     num_tokens: Sequence[int], expert_scale=None) -> List[torch.Tensor]:
     """Expert placeholder + ``combine`` of every rank (reference.py:262, :151-234).
 
     Arrival order at the home rank is expert rank ascending, then local expert,
@@ -248,6 +248,10 @@ def simulate_combine(cfg, world_size: int, disp: Sequence[RankDispatch], weights
     of different tokens never meet.  So each token's K contributions are added
     in ascending order of their global expert id, each add rounded to
     ``out_dtype``; that is K vectorised steps over all tokens.
+
+    ``expert_scale`` (optional, tensor [num_experts] fp32) replaces the placeholder's
+    ``1 + rank`` by a per-expert factor: a stand-in for a real expert op when the
+    expert hook of the library is tested.
     """
     H = cfg.hidden_dim
     ys = [torch.zeros(n, H, dtype=cfg.out_dtype) for n in num_tokens]
@@ -255,7 +259,11 @@ def simulate_combine(cfg, world_size: int, disp: Sequence[RankDispatch], weights
     per_home_rows = [[] for _ in range(world_size)]
     per_home_meta = [[] for _ in range(world_size)]
     for d in range(world_size):
-        y = (disp[d].rows.to(cfg.out_dtype).to(torch.float32) * float(1 + d)).to(cfg.out_dtype)  # :262
+        if expert_scale is None:
+            y = (disp[d].rows.to(cfg.out_dtype).to(torch.float32) * float(1 + d)).to(cfg.out_dtype)  # :262
+        else:
+            f = expert_scale.to(torch.float32)[disp[d].meta[:, 0].to(torch.int64)]
+            y = (disp[d].rows.to(cfg.out_dtype).to(torch.float32) * f[:, None]).to(cfg.out_dtype)
         src = disp[d].meta[:, 1].to(torch.int64)
         for h in range(world_size):
             sel = (src == h).nonzero(as_tuple=True)[0]
@@ -283,13 +291,13 @@ def simulate_combine(cfg, world_size: int, disp: Sequence[RankDispatch], weights
     return ys
 
 
-def simulate(cfg, world_size: int, rank_datas) -> "tuple[List[RankDispatch], List[torch.Tensor]]":
+def simulate(cfg, world_size: int, rank_datas, expert_scale=None) -> "tuple[List[RankDispatch], List[torch.Tensor]]":
     """``ref_kernel`` (reference.py:256-272) for every rank: dispatch results and outputs."""
     xs = [rd.x.cpu() for rd in rank_datas]
     idx = [rd.indices.cpu() for rd in rank_datas]
     disp = simulate_dispatch(cfg, world_size, xs, idx)
     ys = simulate_combine(cfg, world_size, disp, [rd.weights for rd in rank_datas],
-                          [rd.num_tokens for rd in rank_datas])
+                          [rd.num_tokens for rd in rank_datas], expert_scale)
     return disp, ys
 
 

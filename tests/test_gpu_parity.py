@@ -398,3 +398,37 @@ def test_reference_task_shapes_fp16(spec):
             torch.testing.assert_close(out[r].cpu().float(), ys[r].float(), rtol=1e-2, atol=5e-3)
     finally:
         world.close()
+
+
+@pytest.mark.parametrize("payload", ["direct", "dedup"])
+def test_real_expert_hook_between_dispatch_and_combine(payload):
+    """The hook for a real expert op: after dispatch_recv the caller overwrites the valid slab rows in
+    place with its own kernel (here: a per-expert factor, in torch), calls expert_done instead of the
+    placeholder, and combine pulls what the caller wrote."""
+    ws, E, K, H, T = 2, 8, 3, 256, 24
+    datas = [pkg.generate_input(E, K, H, T, seed=31, rank=r, world_size=ws, ragged=True) for r in range(ws)]
+    cfg = datas[0][0]
+    rds_cpu = [d[1] for d in datas]
+    factor = torch.arange(E, dtype=torch.float32) * 0.5 + 1.5  # one factor per global expert
+    _, ys = O.simulate(cfg, ws, rds_cpu, expert_scale=factor)
+    world = LocalWorld(cfg, ws, payload=payload)
+    try:
+        rds = [rd.to(DEV) for rd in rds_cpu]
+        world.dispatch(rds)  # route + send + recv on every rank
+        L = E // ws
+        for r, c in enumerate(world.ctxs):
+            rows, counts = c.expert_buffers()
+            assert rows.shape == (L, ws, T, H) and counts.shape == (ws, 4, L)
+            n = counts[:, 0, :].cpu()  # single chunk: entry 0 is the number of valid rows of slab (l, s)
+            for l in range(L):
+                for s in range(ws):
+                    v = int(n[s, l])
+                    rows[l, s, :v] = (rows[l, s, :v].float() * float(factor[r * L + l])).to(cfg.in_dtype)
+            c.expert_done()
+        out = [c.combine(rd.weights) for c, rd in zip(world.ctxs, rds)]
+        torch.cuda.synchronize()
+        world.check()
+        for r in range(ws):
+            torch.testing.assert_close(out[r].cpu().float(), ys[r].float(), rtol=2e-2, atol=2e-2)
+    finally:
+        world.close()
