@@ -266,6 +266,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if ws > 1:
+        # keep stdout to the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) goes there too
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=dev)
 
     wl = pkg.WORKLOADS[args.workload]
