@@ -303,10 +303,14 @@ _original_destroy = dist.destroy_process_group
 
 
 def _destroy_with_release(*args, **kwargs):
+    error = None
     try:
         release_contexts(barrier=True)
-    finally:
-        return _original_destroy(*args, **kwargs)
+    except Exception as e:  # noqa: BLE001 - the group must still be destroyed; re-raised below
+        error = e
+    _original_destroy(*args, **kwargs)
+    if error is not None:
+        raise error
 
 
 def install_process_group_hooks() -> None:
