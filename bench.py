@@ -45,11 +45,16 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c4")
     ap.add_argument("--payload", default=None, help="direct | dedup | fp8 (default: the workload's own)")
+    ap.add_argument("--schedule", default=None, help="pipelined | phased (default: pipelined where the payload allows)")
+    ap.add_argument("--combine", default=None, help="push | pull (default: push with the pipelined schedule)")
+    ap.add_argument("--senders", type=int, default=0, help="sender blocks of the pipelined kernel (0: library default)")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--verify", action="store_true",
-                    help="after timing, check one forward of every rank against the CPU checker (rank 0 computes it)")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="skip the check of one forward of every rank (dispatch digests and outputs) against the CPU checker")
+    ap.add_argument("--skip-link-probe", action="store_true")
+    ap.add_argument("--trace", default=None, help="write the merged in-kernel trace of one forward (chrome JSON) here")
     ap.add_argument("--per-phase-launches", action="store_true",
-                    help="run the forward as one kernel per phase instead of one cooperative launch")
+                    help="phased schedule: run the forward as one kernel per phase instead of one cooperative launch")
     return ap.parse_args()
 
 
@@ -219,7 +224,7 @@ def reference_main(args, rank: int, ws: int):
         "impl": "reference", "metric": METRIC, "value": us, "unit": "us", "n_gpus": ws, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.workload, ws, "dedup"),
+        "config": workload_config(args.workload, ws, "n/a (CPU)", "n/a (CPU)"),
         "cpu_baseline": {"value": us, "unit": "us", "cores": min(cores, ws * threads), "kind": "port", "sample": sample},
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -241,6 +246,11 @@ def workload_config(name: str, ws: int, payload: str, launches: str = "one coope
     }
 
 
+def percentile(values, q):
+    v = sorted(values)
+    return v[min(len(v) - 1, int(round(q * (len(v) - 1))))]
+
+
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
@@ -258,7 +268,7 @@ def main():
     import torch.distributed as dist
 
     import gpu_mode_kernels_b200 as pkg
-    from gpu_mode_kernels_b200 import traffic
+    from gpu_mode_kernels_b200 import traffic, verify
     from gpu_mode_kernels_b200.all2all import A2AContext
 
     if not torch.cuda.is_available():
@@ -273,13 +283,17 @@ def main():
 
     wl = pkg.WORKLOADS[args.workload]
     payload = args.payload or wl.get("payload", "dedup")
+    schedule = args.schedule or ("pipelined" if payload == "dedup" else "phased")
+    combine = args.combine or ("push" if schedule == "pipelined" else "pull")
     cfg, rd_cpu, _, _ = pkg.workload_input(args.workload, rank, ws)
     rd = rd_cpu.to(dev)
     T, K, H = rd.num_tokens, cfg.experts_per_token, cfg.hidden_dim
-    ctx = A2AContext(cfg, rank, ws, device=local_rank, payload=payload)
-    if args.per_phase_launches:
+    ctx = A2AContext(cfg, rank, ws, device=local_rank, payload=payload, schedule=schedule, combine=combine,
+                     senders=args.senders)
+    pipelined = schedule == "pipelined"
+    if args.per_phase_launches and not pipelined:
         ctx.set_fused(False)
-    fused = not args.per_phase_launches
+    fused = pipelined or not args.per_phase_launches
     y = torch.empty(T, H, dtype=cfg.out_dtype, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
     stream = torch.cuda.current_stream()
@@ -320,6 +334,8 @@ def main():
         per_step_ms, launches = timed_loop(lambda: ctx.forward(rd.x, rd.indices, rd.weights, y), args.steps, args.warmup)
     ctx.check()
     ms = sum(per_step_ms) / len(per_step_ms)
+    if ws > 1:
+        launches -= args.steps  # the device-side rendezvous before every step is not part of the path
 
     # ---- end to end: host buffers through the plugin-facing entry --------
     hx, hi, hw = rd_cpu.x.pin_memory(), rd_cpu.indices.pin_memory(), rd_cpu.weights.pin_memory()
@@ -331,24 +347,26 @@ def main():
     h2d = hx.numel() * hx.element_size() + hi.numel() * 4 + hw.numel() * 4
     d2h = hy.numel() * hy.element_size()
 
-    # ---- per-kernel pass: events between the four launches ---------------
+    # ---- per-kernel pass: events between the separate launches of the same device code ----
     ph_steps = min(args.steps, 200)
-    names = ["route", "dispatch_send", "recv_expert", "combine"]
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(ph_steps)]
+    if pipelined:
+        names = ["send_route", "expert", "combine"]
+        calls = [lambda: ctx.pipe_step(0, rd.x, rd.indices, rd.weights), lambda: ctx.pipe_step(1),
+                 lambda: ctx.pipe_step(2, y=y)]
+    else:
+        names = ["route", "dispatch_send", "recv_expert", "combine"]
+        calls = [lambda: ctx.route(rd.indices), lambda: ctx.dispatch_send(rd.x), ctx.dispatch_recv_expert,
+                 lambda: ctx.combine(rd.weights, y)]
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] for _ in range(ph_steps)]
     for i in range(ph_steps + 5):
         flush.fill_(i & 1)
         if ws > 1:
             ctx.barrier()
         e = evs[i - 5] if i >= 5 else None
-        if e: e[0].record(stream)
-        ctx.route(rd.indices)
-        if e: e[1].record(stream)
-        ctx.dispatch_send(rd.x)
-        if e: e[2].record(stream)
-        ctx.dispatch_recv_expert()
-        if e: e[3].record(stream)
-        ctx.combine(rd.weights, y)
-        if e: e[4].record(stream)
+        for j, fn in enumerate(calls):
+            if e: e[j].record(stream)
+            fn()
+        if e: e[len(calls)].record(stream)
     sync_all()
     ctx.check()
     phase_us = {}
@@ -356,37 +374,53 @@ def main():
         per = max_over_ranks([e[j].elapsed_time(e[j + 1]) for e in evs])
         phase_us[n] = 1e3 * sum(per) / len(per)
 
+    # ---- measured peer-copy bandwidth of this box (every rank copies to its neighbour at once) ----
+    link = None
+    if ws > 1 and not args.skip_link_probe:
+        nbytes = min(256 << 20, T * ws * (cfg.num_experts // ws) * H * 2)
+        reps = 10
+        for _ in range(2):
+            ctx.link_probe((rank + 1) % ws, nbytes)
+        sync_all()
+        ctx.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            ctx.link_probe((rank + 1) % ws, nbytes)
+        b.record(stream)
+        sync_all()
+        t_ms = max_over_ranks([a.elapsed_time(b)])[0]
+        link = {"peer_copy_gbs": nbytes * reps / (t_ms * 1e-3) / 1e9, "bytes": nbytes, "copies": reps,
+                "how": "cudaMemcpyAsync device-to-device into the next rank's region, all ranks at once, CUDA events, "
+                       "max over ranks"}
+
     # ---- traffic and roofline --------------------------------------------
     hbm_peak, peak_kind = measured_peaks()
     all_idx = [pkg.workload_input(args.workload, r, ws)[1].indices for r in range(ws)] if ws > 1 else [rd_cpu.indices]
-    tr = traffic.summarize(all_idx, cfg.num_experts, ws, H, payload)
+    tr = traffic.summarize(all_idx, cfg.num_experts, ws, H, payload, combine)
     if ws == 1:
-        alg = traffic.hbm_bytes_single_rank(T, K, H)
-        per_kernel = {n: {"us": phase_us[n], "algorithmic_bytes": alg[n],
-                          "gbs": alg[n] / (phase_us[n] * 1e-6) / 1e9} for n in names}
-        if fused:
-            # one launch does everything: rows written and read in dispatch, read in combine, y written
-            dom, dom_bytes, dom_us = "forward_kernel (route+send+expert+combine, one launch)", (3 * T * K + T) * 2 * H, ms * 1e3
-        else:
-            dom = max(names, key=lambda n: phase_us[n])
-            dom_bytes, dom_us = alg[dom], phase_us[dom]
-        achieved = dom_bytes / (dom_us * 1e-6) / 1e9
-        roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                    "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                    "algorithmic_bytes": dom_bytes, "kernel_us": dom_us, "per_phase_kernels": per_kernel,
-                    "traffic_note": "null on purpose: ncu replays the launch with its 33 MB working set resident in the "
-                                    "126 MB L2 (7.8 MB DRAM, 100 MB L2 traffic per launch, profiles/forward_kernel_c4_world1.md), "
-                                    "which says nothing about the flushed-L2 launches timed here"}
+        alg = (3 * T * K + T) * 2 * H  # rows written and read in dispatch, read in combine, y written
+        achieved = alg / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "one-launch forward (route + send + expert + combine)",
+                    "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                    "traffic": SINGLE_GPU_TRAFFIC.get((args.workload, schedule, combine)),
+                    "peak_kind": f"of {peak_kind}", "algorithmic_bytes": alg, "kernel_us": ms * 1e3,
+                    "traffic_note": "bytes per launch from one ncu capture of this kernel on this workload "
+                                    "(dram__bytes_read.sum + dram__bytes_write.sum; L2 traffic beside it): the working set "
+                                    "fits the 126 MB L2, so DRAM sees far less than the algorithmic bytes"}
         nvlink = None
     else:
         achieved = tr["algorithmic_bytes"] / (ms * 1e-3) / 1e9
-        roofline = {"bound": "nvlink", "kernel": "dispatch_send+combine", "achieved": achieved,
-                    "peak": traffic.NVLINK_MEASURED_GBS, "unit": "GB/s", "frac": achieved / traffic.NVLINK_MEASURED_GBS,
-                    "traffic": None, "peak_kind": "of measured peer copy (770 GB/s per direction)",
-                    "algorithmic_bytes": tr["algorithmic_bytes"]}
+        roofline = {"bound": "nvlink", "kernel": "one-launch forward (dispatch + combine transfers)", "achieved": achieved,
+                    "peak": traffic.NVLINK_NOMINAL_GBS, "unit": "GB/s", "frac": achieved / traffic.NVLINK_NOMINAL_GBS,
+                    "traffic": None, "peak_kind": "of nominal NVLink 5 per direction (900 GB/s)",
+                    "algorithmic_bytes": tr["algorithmic_bytes"], "wire_bytes": tr["wire_bytes"],
+                    "wire_gbs": tr["wire_bytes"] / (ms * 1e-3) / 1e9,
+                    "wire_frac": tr["wire_bytes"] / (ms * 1e-3) / 1e9 / traffic.NVLINK_NOMINAL_GBS}
         nvlink = {"algorithmic_gbs": achieved, "frac_of_900": achieved / traffic.NVLINK_NOMINAL_GBS,
-                  "wire_gbs": tr["wire_bytes"] / (ms * 1e-3) / 1e9, "busiest_rows": tr["busiest_rows"],
-                  "busiest_rows_dedup": tr["busiest_rows_dedup"], "t_roof_us_900": tr["t_roof_us_nominal"]}
+                  "wire_gbs": roofline["wire_gbs"], "busiest_rows": tr["busiest_rows"],
+                  "busiest_rows_dedup": tr["busiest_rows_dedup"], "t_roof_us_900": tr["t_roof_us_nominal"],
+                  "t_wire_us_900": tr["t_wire_us_nominal"], "measured_link": link}
 
     # ---- CPU baseline (rank 0, N=1 only): the port of the reference path --
     cpu_baseline = None
@@ -397,30 +431,73 @@ def main():
                                   f"threads; dispatch+combine of the reference's Python path, best of 3; expert "
                                   f"placeholder on valid rows ({1e3 * min(expert_s):.1f} ms) not counted"}
 
+    # ---- parity of the path that was just timed: one more forward of every rank, checked on rank 0 ----
     verified = None
-    if args.verify:
-        # one more forward; every rank's output goes to rank 0, which alone runs the CPU checker
+    if not args.no_verify:
         yv = ctx.forward(rd.x, rd.indices, rd.weights)
         sync_all()
         ctx.check()
+        counts, rows, meta = ctx.export_dispatch()
+        torch.cuda.synchronize()
+        crows, cmeta = verify.compact_dispatch(counts.cpu(), rows, meta)
+        digest = torch.tensor(verify.dispatch_digest(counts.cpu(), crows, cmeta), dtype=torch.int64, device=dev)
+        del rows, meta, crows, cmeta
         gathered = [torch.empty_like(yv) for _ in range(ws)] if rank == 0 else None
+        digests = [torch.empty_like(digest) for _ in range(ws)] if rank == 0 else None
         if ws > 1:
             dist.gather(yv, gathered, dst=0)
+            dist.gather(digest, digests, dst=0)
         else:
-            gathered = [yv]
+            gathered, digests = [yv], [digest]
         if rank == 0:
             from oracle import a2a_oracle as O
 
             rds = [pkg.workload_input(args.workload, r, ws)[1] for r in range(ws)]
-            _, ys = O.simulate(cfg, ws, rds)
+            disp, ys = O.simulate(cfg, ws, rds)
             tol = 6e-2 if payload == "fp8" else 2e-2
-            worst, outliers = 0.0, 0
+            worst, outliers, dispatch_ok = 0.0, 0, True
             for r in range(ws):
                 d = (gathered[r].cpu().float() - ys[r].float()).abs() / (tol + tol * ys[r].float().abs())
                 worst = max(worst, float(d.max()))
                 outliers += int((d > 1).sum())
-            verified = {"rtol_atol": tol, "worst_diff_over_tol": worst, "elements_outside": outliers,
-                        "ok": bool(worst <= (1.25 if payload == "fp8" else 1.0))}
+                # the one-launch kernels leave the expert OUTPUT of every dispatched row in the slabs:
+                # dtype(float(row) * (1 + rank)), one rounding (FP8: of the dequantised row)
+                erows = disp[r].rows
+                if payload == "fp8" and erows.numel():
+                    q, sc = O.fp8_quantise(erows)
+                    erows = O.fp8_dequantise(q, sc, cfg.in_dtype)
+                erows = (erows.float() * float(1 + r)).to(cfg.in_dtype)
+                want = verify.dispatch_digest(disp[r].expert_num_tokens, erows, disp[r].meta)
+                dispatch_ok = dispatch_ok and tuple(int(v) for v in digests[r].cpu().tolist()) == want
+            verified = {"ok": bool(dispatch_ok and worst <= (1.25 if payload == "fp8" else 1.0)),
+                        "dispatch_bit_exact": bool(dispatch_ok), "rtol_atol": tol, "worst_diff_over_tol": worst,
+                        "elements_outside": outliers,
+                        "how": "one forward of every rank after the timed loops: digests of counts / rows / "
+                               "(expert, source, token, k) records of every rank's slabs against the CPU checker's "
+                               "dispatch, outputs against its combine"}
+        sync_all()
+
+    # ---- in-kernel trace of one forward, merged over the ranks -----------
+    if args.trace:
+        from gpu_mode_kernels_b200 import trace as tracing
+
+        ctx.trace_enable(True)
+        if ws > 1:
+            ctx.barrier()
+        ctx.forward(rd.x, rd.indices, rd.weights, y)
+        stamps = ctx.trace_read()
+        ctx.trace_enable(False)
+        mine = tracing.rank_events(stamps, rank, sm_mhz=clocks.summary()["sm_mhz"] or 1965.0, world_size=ws,
+                                   pipelined=pipelined)
+        everyone = [None] * ws
+        if ws > 1:
+            dist.gather_object(mine, everyone if rank == 0 else None, dst=0)
+        else:
+            everyone = [mine]
+        if rank == 0:
+            tracing.write_chrome_trace(args.trace, everyone)
+            with open(os.path.splitext(args.trace)[0] + "_summary.txt", "w") as f:
+                f.write(tracing.summarize(everyone))
         sync_all()
 
     if rank == 0:
@@ -433,8 +510,11 @@ def main():
             "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches, "clocks": clocks.summary(),
             "kernels_us": phase_us, "tokens_per_s": T * ws / (ms * 1e-3),
-            "p50_us": 1e3 * statistics.median(per_step_ms), "max_us": 1e3 * max(per_step_ms),
+            "p50_us": 1e3 * statistics.median(per_step_ms), "p95_us": 1e3 * percentile(per_step_ms, 0.95),
+            "max_us": 1e3 * max(per_step_ms),
         }
+        line["config"]["schedule"] = schedule
+        line["config"]["combine"] = combine
         if nvlink is not None:
             line["nvlink"] = nvlink
         if verified is not None:
@@ -445,6 +525,14 @@ def main():
     ctx.close()
     if ws > 1:
         dist.destroy_process_group()
+    if verified is not None and rank == 0 and not verified["ok"]:
+        sys.exit(3)
+
+
+# DRAM and L2 bytes per launch of the one-launch kernel at world size 1, from the ncu captures
+# summarised under profiles/ (a profiler cannot run inside the timed loop, so the figures are
+# constants of the kernel + workload, re-measured whenever the kernel changes).
+SINGLE_GPU_TRAFFIC = {}
 
 
 if __name__ == "__main__":

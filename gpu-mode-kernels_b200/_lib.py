@@ -15,13 +15,15 @@ LIB_PATH = os.path.join(PKG_DIR, "liba2a.so")
 A2A_OK, A2A_ERR_CONFIG, A2A_ERR_CAPACITY, A2A_ERR_TIMEOUT, A2A_ERR_STATE, A2A_ERR_ROUTING = range(6)
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 PAYLOAD = {"direct": 0, "dedup": 1, "fp8": 2}
+SCHEDULE = {"phased": 0, "pipelined": 1}
+COMBINE = {"pull": 0, "push": 1}
 MAX_WORLD, MAX_EXPERTS, MAX_TOPK = 8, 1024, 32
 
 
 class Config(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "rank", "world_size", "device", "num_experts", "experts_per_token", "hidden_dim",
-        "max_num_tokens", "dtype", "payload", "timeout_ms")]
+        "max_num_tokens", "dtype", "payload", "timeout_ms", "schedule", "combine", "chunks", "senders")]
 
 
 class Status(C.Structure):
@@ -43,7 +45,11 @@ SIGNATURES = {
     "a2a_destroy": (_I, [_VP]),
     "a2a_ipc_handle_bytes": (C.c_size_t, []),
     "a2a_export_handle": (_I, [_VP, _VP]),
-    "a2a_open_peers": (_I, [_VP, _VP]),
+    "a2a_open_peers": (_I, [_VP, _VP, C.c_size_t]),
+    "a2a_last_error": (C.c_char_p, [_VP]),
+    "a2a_fingerprint": (_I, [C.POINTER(Config), _VP]),
+    "a2a_check_handles": (_I, [C.POINTER(Config), _VP, C.c_size_t, C.c_char_p, C.c_size_t]),
+    "a2a_pipe_step": (_I, [_VP, _I, _VP, _VP, _VP, _VP, _I, _VP]),
     "a2a_attach_local_peers": (_I, [_VP, C.POINTER(_VP)]),
     "a2a_route": (_I, [_VP, _VP, _I, _VP]),
     "a2a_dispatch_send": (_I, [_VP, _VP, _VP]),
@@ -56,6 +62,7 @@ SIGNATURES = {
     "a2a_set_fused": (_I, [_VP, _I]),
     "a2a_forward_host": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _VP]),
     "a2a_barrier": (_I, [_VP, _VP]),
+    "a2a_link_probe": (_I, [_VP, _I, C.c_size_t, _VP]),
     "a2a_export_dispatch": (_I, [_VP, _VP, _VP, _VP, _VP]),
     "a2a_expert_buffers": (_I, [_VP, C.POINTER(_VP), C.POINTER(_VP)]),
     "a2a_route_buffers": (_I, [_VP, C.POINTER(_VP), C.POINTER(_VP)]),
@@ -63,6 +70,7 @@ SIGNATURES = {
     "a2a_route_noalloc": (_I, [_VP, _I, _I, _I, _VP, _VP, _VP]),
     "a2a_status": (_I, [_VP, C.POINTER(Status)]),
     "a2a_status_clear": (_I, [_VP]),
+    "a2a_status_peek": (_I, [_VP]),
     "a2a_trace_enable": (_I, [_VP, _I]),
     "a2a_trace_read": (_I, [_VP, _VP, _I, C.POINTER(_I), C.POINTER(_I)]),
     "a2a_launch_count": (C.c_int64, [_VP]),

@@ -14,17 +14,17 @@
 //     relaxed system-scope stores of this call's epoch into one flag word per peer;
 //   * on the consumer GPU one "watcher" thread per flag polls it with relaxed system-scope
 //     loads (strong, L1-bypassing; an acquire load per poll would run a fence per
-//     iteration) and re-publishes it in a local word with a gpu-scope fence + release;
-//     everybody else waits on the local word at gpu scope.  The consumer side deliberately
-//     has no system-scope fence: with peers mapped, a fence.sys is a flush round trip over
-//     NVLink that queues behind the row traffic (5-15 us when measured), and it protects
-//     nothing here -- the producer's fence.sys completed only after its rows were performed
-//     in OUR L2, and every later read of those rows bypasses L1.  This is the discipline
-//     NCCL's primitives use as well (system fence on the posting side only).
+//     iteration), takes ONE system-scope acquire fence once the flag has arrived (so the
+//     producer's release and this acquire are a morally strong pair under the PTX model)
+//     and re-publishes the flag in a local word with a gpu-scope release; everybody else
+//     waits on the local word at gpu scope and reads the rows with L1-bypassing loads.
+//     Only the watcher threads (at most one per peer and flag kind) ever execute a
+//     system-scope fence on the consumer side: a fence.sys in every waiting block is a
+//     flush round trip over NVLink that queues behind the row traffic.
 // The PTX memory model makes causality order transitive across edges of different scope,
 // so a row stored by any block of GPU A is visible to any block of GPU B that has seen
-// B's local word, with two system fences per GPU and call instead of thousands (none at
-// all on a single GPU).
+// B's local word, with a handful of system fences per GPU and call instead of thousands
+// (none at all on a single GPU).
 // Flags carry a monotonically increasing call number ("epoch"), are never reset, and
 // every (source, destination) pair has its own flag word on its own 128-byte line.
 // Every wait is bounded by a wall-clock budget; on expiry the kernel records
@@ -45,15 +45,25 @@ constexpr int kThreads = 256;    // every kernel of the path runs 256-thread blo
 constexpr int kFlagStride = 32;  // uint32 words between two flags = 128 bytes
 constexpr int kFp8Block = 128;   // elements sharing one fp32 scale
 constexpr int kMaxChunks = 4;    // token chunks a call is pipelined in (whole 32-token bitmap words each)
+constexpr int kStageBytes = 16384;  // one stage of a sender block's shared-memory ring (a row piece)
+constexpr int kStages = 4;          // stages of that ring: two bulk loads and two bulk stores in flight
+constexpr unsigned kNoEntry = 0xffffffffu;  // record entry of a (token, k) pair that has no row on the destination
 enum FlagKind : int { kFlagDispatch = 0, kFlagExpert = 1, kFlagBarrier = 2, kNumFlagKinds = 3 };
 enum Phase : int { kPhaseRoute = 1, kPhaseSend = 2, kPhaseRecv = 3, kPhaseExpert = 4, kPhaseCombine = 5, kPhaseBarrier = 6 };
 // In-kernel trace: thread 0 of every block stamps these points with the SM cycle counter
 // (slot 0 additionally holds the nanosecond global timer so blocks can be aligned).
 enum Ticket : int { kTicketSend = 0, kTicketExpert = 1 };
+// The phase-by-phase kernels stamp slots 1..7; the pipelined kernel additionally stamps, per
+// position i of its source / destination order, when a sender block finished destination i
+// (kStampDestDone + i), when an expert block saw source i's rows (kStampSourceSeen + i) and
+// when it was through with them (kStampSourceDone + i).  kStampRole tells what the block was.
 enum Stamp : int {
     kStampGlobalNs = 0, kStampStart, kStampRouted, kStampSent, kStampDispatchSeen, kStampExpertDone,
-    kStampExpertSeen, kStampCombineDone, kNumStamps = 8
+    kStampExpertSeen, kStampCombineDone, kStampRole = kStampRouted /* pipelined: what the block was */,
+    kStampSourceSeen = 8, kStampSourceDone = 16, kStampDestDone = 24,
+    kNumStamps = 32
 };
+enum Role : int { kRoleSender = 1, kRoleExpert = 2, kRoleRouter = 4, kRoleWatcher = 8 };
 
 // Everything a kernel needs, passed by value (lives in the constant bank).
 struct DevParams {
@@ -64,7 +74,14 @@ struct DevParams {
     size_t off_counts;      // [ws][kMaxChunks][L] int32: rows source s sent to local expert l up to the END of chunk c
     size_t off_flags;       // [kNumFlagKinds][A2A_MAX_WORLD][kFlagStride] u32 epochs, written by the peers
     size_t off_stage;       // [ws][T_max][stage_row_bytes]: one wire row per (source, token)   (DEDUP / FP8)
+    // pipelined schedule only: what a source tells a destination about the wire rows it sends there
+    size_t off_rec_tok;     // [ws][T_max] int32: token of wire row n of source s
+    size_t off_rec_ent;     // [ws][T_max][K] u32: (local expert << 16 | slot) of pair k of that token, or kNoEntry
+    size_t off_rec_w;       // [ws][T_max][K] f32: the token's top-k weights (used when the expert rank reduces)
+    size_t off_hdr;         // [ws][8] int32: [0] = number of wire rows source s sent in this call
+    size_t off_ret;         // [ws][T_max][H] elements: partial sums pushed home by expert rank d (PUSH combine)
     int stage_row_bytes;
+    int senders;            // blocks of the pipelined kernel that only move rows to the peers
     int rank, ws, E, K, H, T_max, L;
     int T;                  // tokens of this rank in the current call
     int chunks;             // token chunks per call, 1..kMaxChunks (same on every rank)
@@ -75,6 +92,7 @@ struct DevParams {
     int* slot;              // [T_max*K] slot of pair (t,k) inside slab (expert, this rank), -1 = dropped
     int* send_counts;       // [E]
     uint32_t* tickets;      // [2][kMaxChunks] block-arrival counters, one per publishing phase and chunk
+    uint32_t* ptickets;     // [2][A2A_MAX_WORLD] pipelined schedule: arrivals per destination / per source
     uint32_t* seen;         // [2][A2A_MAX_WORLD][kFlagStride] local re-publication of the peers' dispatch / expert flags
     a2a_status_t* status;
     long long* trace;       // [blocks][kNumStamps] or nullptr when tracing is off
@@ -96,6 +114,11 @@ __device__ __forceinline__ void stamp(const DevParams& p, int which) {
         p.trace[(size_t)blockIdx.x * kNumStamps + which] = clock64();
         if (which == kStampStart) p.trace[(size_t)blockIdx.x * kNumStamps + kStampGlobalNs] = global_ns();
     }
+}
+
+// Value stamp (not a time): e.g. the role of the block.
+__device__ __forceinline__ void stamp_value(const DevParams& p, int which, long long v) {
+    if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * kNumStamps + which] = v;
 }
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -153,6 +176,18 @@ __device__ __forceinline__ float ld_stream(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcg(p, v); }
 __device__ __forceinline__ void st_stream(uint2* p, uint2 v) { __stcg(p, v); }
 
+// The status record in device memory, followed by the address of a word in mapped host memory
+// that mirrors `code`: the host can see that something was recorded without any CUDA call.
+struct StatusBlock {
+    a2a_status_t s;
+    int* host_code;
+};
+
+__device__ __forceinline__ void mirror_code(a2a_status_t* st, int code) {
+    int* host = reinterpret_cast<StatusBlock*>(st)->host_code;
+    if (host != nullptr) *reinterpret_cast<volatile int*>(host) = code;
+}
+
 __device__ __forceinline__ void record_error(a2a_status_t* st, int code, int rank, int peer, int phase,
                                              uint32_t epoch, int detail) {
     if (atomicCAS(&st->code, 0, code) == 0) {
@@ -161,6 +196,7 @@ __device__ __forceinline__ void record_error(a2a_status_t* st, int code, int ran
         st->phase = phase;
         st->epoch = epoch;
         st->detail = detail;
+        mirror_code(st, code);
         __threadfence();
     }
 }
@@ -177,6 +213,7 @@ __device__ __forceinline__ void record_timeout(const DevParams& p, int phase, in
         p.status->phase = phase;
         p.status->epoch = epoch;
         p.status->detail = 0;
+        mirror_code(p.status, A2A_ERR_TIMEOUT);
         __threadfence();
     }
 }
@@ -209,9 +246,10 @@ __device__ __forceinline__ bool wait_epoch(Load load, Acquire acquire, uint32_t 
     }
 }
 
-// A flag another GPU writes: polled with strong system-scope loads; gpu-scope fence on success.
+// A flag another GPU writes: polled with strong system-scope loads; ONE system-scope acquire
+// fence on success (only watcher threads and the barrier kernel come through here).
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch, const DevParams& p, int phase, int peer) {
-    return wait_epoch([flag] { return ld_relaxed_sys(flag); }, [] { fence_acq_rel_gpu(); }, epoch, p, phase, peer);
+    return wait_epoch([flag] { return ld_relaxed_sys(flag); }, [] { fence_acq_rel_sys(); }, epoch, p, phase, peer);
 }
 
 // A word a thread of this GPU writes: gpu scope.
@@ -300,6 +338,69 @@ __device__ __forceinline__ int upper_slab(const int* prefix, int n, int r) {
     }
     return lo;
 }
+
+// ---- bulk asynchronous copies (the copy engine of the SM) and their mbarriers ----------
+// Only the plain forms are used: one CTA's shared memory, no cluster-wide delivery.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+// Makes the initialised barriers visible to the copy engine.
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// global -> this CTA's shared memory; completion is counted in bytes on `bar`.
+// dst, src and bytes must be multiples of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// this CTA's shared memory -> global (local or a peer's); joins the thread's current bulk group.
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// At most N of this thread's most recent bulk groups may still be READING shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+
+// At most n (0..3; larger waits for 3) of this thread's most recent bulk groups may still be pending
+// at all: the older ones have written their destination.
+__device__ __forceinline__ void bulk_wait_done(int n) {
+    switch (n) {
+        case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
+        default: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+    }
+}
+
+// Orders the copy engine's accesses to global memory with this thread's ordinary ones.
+__device__ __forceinline__ void fence_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+// ... and its reads of shared memory after ordinary stores to it.
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- element types ---------------------------------------------------------
 template <typename T> struct Vec2;

@@ -392,23 +392,25 @@ __device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem
 // token's output.  Lane k < K looks up pair (t,k): expert, slot (known from routing,
 // so no metadata is fetched), weight, and waits (bounded) until the expert's rank has
 // published its outputs -- warp d of the grid is the watcher of rank d's flag, the
-// others wait on the local word.  Pointer and weight are then broadcast by shuffles and
+// others wait on the local word; only then is the pair's slot read.  Pointer and weight are then broadcast by shuffles and
 // every lane pulls its 16 bytes of each of the K rows from the rank that holds them,
 // four loads in flight, accumulating float(row) * w in fp32 in k order.
 // ---------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void combine_phase(const DevParams& p) {
+__device__ __forceinline__ void combine_phase(const DevParams& p, int cb, int ncb, bool own_watchers) {
     const int lane = threadIdx.x & 31;
-    const int warp = (int)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
-    const int nwarps = (int)gridDim.x * (kThreads / 32);
+    const int warp = cb * (kThreads / 32) + (threadIdx.x >> 5);
+    const int nwarps = ncb * (kThreads / 32);
     const int K = p.K, nvec = p.H >> 3;
     const int nseg = (nvec + 31) >> 5;
     for (int c = 0; c < p.chunks; ++c) {
     const uint32_t want = flag_value(p, c);
     const int ta = chunk_begin(p, c), tb = chunk_end(p, c);
     const int items = (tb - ta) * nseg;
-    // warp d of the grid watches rank d's flag for this chunk before its own items
-    if (warp < p.ws && warp != p.rank && lane == 0) watch_and_republish(p, kFlagExpert, warp, kPhaseCombine, want);
+    // warp d of the grid watches rank d's flag for this chunk before its own items (unless the
+    // caller has watchers of its own)
+    if (own_watchers && warp < p.ws && warp != p.rank && lane == 0)
+        watch_and_republish(p, kFlagExpert, warp, kPhaseCombine, want);
     __syncwarp();
     unsigned ready = 0u;  // ranks this lane has already seen ready for this chunk
     for (int item = warp; item < items; item += nwarps) {
@@ -419,17 +421,22 @@ __device__ __forceinline__ void combine_phase(const DevParams& p) {
         bool ok = true;
         if (lane < K) {
             const size_t pair = (size_t)t * K + lane;
-            const int j = ld_stream(p.slot + pair);
-            if (j >= 0) {
-                const int e = __ldg(p.idx + pair);
+            const int e = __ldg(p.idx + pair);
+            if (e >= 0 && e < p.E) {
+                // The expert's rank is known from the caller's indices alone.  Its flag is awaited BEFORE
+                // the slot table is read: the flag implies that this rank's own routing of this call (which
+                // other blocks of this grid may still be writing) was complete when the rows left.
                 const int d = e / p.L, l = e - d * p.L;
-                my_w = __ldg(p.w + pair);
-                my_row = reinterpret_cast<unsigned long long>(
-                    reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
-                    (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec);
                 if (!((ready >> d) & 1u)) {
                     ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), want, p, kPhaseCombine, d);
                     ready |= 1u << d;
+                }
+                const int j = ok ? ld_stream(p.slot + pair) : -1;
+                if (j >= 0) {
+                    my_w = __ldg(p.w + pair);
+                    my_row = reinterpret_cast<unsigned long long>(
+                        reinterpret_cast<const uint4*>(p.peer[d] + p.off_rows) +
+                        (((size_t)l * p.ws + p.rank) * p.T_max + j) * nvec);
                 }
             }
         }
@@ -496,7 +503,7 @@ __global__ void __launch_bounds__(kThreads) expert_kernel(const __grid_constant_
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads) combine_kernel(const __grid_constant__ DevParams p) {
-    combine_phase<T>(p);
+    combine_phase<T>(p, (int)blockIdx.x, (int)gridDim.x, true);
 }
 
 // The whole path in one launch.  Launched cooperatively so that every block is
@@ -519,7 +526,7 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(const __grid_constant
     stamp(p, kStampSent);
     expert_chunk<T, PAYLOAD, true, true, true, true>(p, s, p.chunks - 1);
     stamp(p, kStampExpertDone);
-    combine_phase<T>(p);
+    combine_phase<T>(p, (int)blockIdx.x, (int)gridDim.x, true);
 }
 
 // ---------------------------------------------------------------------------

@@ -1,0 +1,651 @@
+// The pipelined schedule: the whole path in ONE cooperative launch whose blocks have
+// fixed roles that run concurrently, so the NVLink transfers of dispatch and combine, the
+// expert pass and the routing tables overlap instead of following each other.
+//
+//   senders  (p.senders blocks; one thread each drives the SM's copy engine)
+//            For destination rank d = rank+1, rank+2, ... (a ring: at any moment every
+//            rank sends to a different peer) the token rows wanted by d are bulk-loaded
+//            from HBM into a four-stage shared-memory ring and bulk-stored straight into
+//            d's stage buffer, one wire row per (token, destination).  No routing table is
+//            needed for that, so rows move from the first microsecond.  When a
+//            destination's last store has completed the block draws a ticket; the last
+//            ticket (all senders + that destination's router) publishes the dispatch flag.
+//   routers  (one block per destination, then they join the experts)
+//            build the [token x expert] bitmap of the destination's experts only, derive
+//            the slot of every (token, k) row by popc, and write the destination its
+//            records: per wire row the token, the (local expert, slot) of each pair and the
+//            token's weights; plus per-slab counts and the (token, k) word of every slab row.
+//   experts  (all other blocks) take the sources in arrival order (own rank first, then
+//            rank-1, rank-2, ...).  Per wire row: read it once, write each slab row it
+//            stands for (the dispatch output) with the placeholder expert op applied, and
+//            -- PUSH combine -- accumulate w[t,k] * row in fp32 and store ONE partial row
+//            per (token, this rank) into the home rank's return buffer over NVLink.  The
+//            block that finishes a source last publishes the expert flag to that source.
+//   watchers (spare warps of sender blocks 0 and 1) poll the peers' flags at system scope
+//            and hand them to the rest of the GPU through local words.
+//   combine  (every block, once its role is done) PUSH: y[t] = sum over the ranks that hold
+//            experts of t of their partial rows, read from local memory.  PULL: each
+//            (token, k) row is pulled from the expert's slab over NVLink and reduced with
+//            the token's weights at home (the phase-by-phase combine, started per peer).
+//
+// Nothing here waits on work of its own role on another GPU, senders and routers never wait
+// at all, and every wait is bounded; see a2a_device.cuh for the flag protocol.
+#pragma once
+
+#include "a2a_kernels.cuh"
+
+namespace a2a {
+
+enum PipeTicket : int { kPipeTicketDest = 0, kPipeTicketSource = 1 };
+
+// ---- shared memory of a block, carved per role --------------------------------------------
+// sender: ring [kStages][kStageBytes] | mbarriers [kStages] u64 | descriptors | list [ws][per] u16 | warp totals
+// router: bits [Wc][L] | wpre [Wc][L] | cnt [L] | warp totals
+__host__ __device__ inline int pipe_list_per(int T_max, int senders) { return (T_max + senders - 1) / (senders > 0 ? senders : 1); }
+
+__host__ __device__ inline size_t pipe_sender_smem(int T_max, int ws, int senders) {
+    size_t b = (size_t)kStages * kStageBytes + 128;                       // ring + barriers
+    b += (size_t)kStages * 32;                                            // descriptors
+    b += ((size_t)ws * pipe_list_per(T_max, senders) * 2 + 15) / 16 * 16; // token lists
+    b += 8 * A2A_MAX_WORLD * 4;                                           // warp totals
+    return b;
+}
+
+__host__ __device__ inline size_t pipe_router_smem(int T_max, int L) {
+    const size_t W = (size_t)(T_max + 31) / 32;
+    return (2 * W * L + L + 16) * 4;
+}
+
+struct SendDesc {
+    unsigned long long dst;  // destination address of the piece
+    unsigned bytes;
+    int dest_done;           // >= 0: this piece is the block's last one for that destination rank
+};
+
+// Ranks whose experts token t uses (in-range pairs only; a repeated expert adds no new rank).
+__device__ __forceinline__ unsigned dest_mask(const DevParams& p, int t) {
+    unsigned m = 0;
+    const int* row = p.idx + (size_t)t * p.K;
+    for (int k = 0; k < p.K; ++k) {
+        const int e = __ldg(row + k);
+        if (e >= 0 && e < p.E) m |= 1u << (e / p.L);
+    }
+    return m;
+}
+
+// One arrival of a sender thread or a router block on destination d's ticket; the last of
+// the `expected` arrivals publishes this rank's dispatch flag on d.  Called by ONE thread
+// whose own stores (and, through a barrier, its block's) are complete.
+__device__ __forceinline__ void arrive_dest(const DevParams& p, int d, uint32_t expected) {
+    fence_async_global();  // bulk stores of this thread, completed above, before the ordinary fence
+    __threadfence();
+    uint32_t* ticket = p.ptickets + kPipeTicketDest * A2A_MAX_WORLD + d;
+    if (atomicAdd(ticket, 1u) == expected - 1) {
+        *ticket = 0;  // everyone has arrived: re-arm for the next call
+        fence_acq_rel_sys();
+        st_relaxed_sys(flag_ptr(p.peer[d], p.off_flags, kFlagDispatch, p.rank), flag_value(p, 0));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Watchers: warp i (lane 0) of the calling set polls the flag of `kind` written by the
+// i-th peer after this rank and republishes it for the GPU.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void watcher_role(const DevParams& p, int kind, int phase, int set_warp) {
+    if ((threadIdx.x & 31) != 0 || set_warp < 0 || set_warp >= p.ws - 1) return;
+    const int peer = (p.rank + 1 + set_warp) % p.ws;
+    watch_and_republish(p, kind, peer, phase, flag_value(p, 0));
+}
+
+// ---------------------------------------------------------------------------
+// Sender block `sb` of `ns`.  All threads build the block's token lists; then thread 0
+// drives the copy engine while, if `watch_kind` >= 0, warps 1.. watch the peers' flags of
+// that kind (they start only after the set-up barrier: a watcher may wait for a long time).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, int sb, int ns, int watch_kind,
+                                            int watch_phase) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = pipe_list_per(p.T_max, ns);
+    uint8_t* ring = smem;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)kStages * kStageBytes);
+    SendDesc* desc = reinterpret_cast<SendDesc*>(smem + (size_t)kStages * kStageBytes + 128);
+    unsigned short* list = reinterpret_cast<unsigned short*>(desc + 2 * kStages);
+    int* wt = reinterpret_cast<int*>(smem + pipe_sender_smem(p.T_max, p.ws, ns) - 8 * A2A_MAX_WORLD * 4);
+    __shared__ int s_cnt[A2A_MAX_WORLD];
+
+    // ---- this block's share of every destination's token list (ballot / popc compaction) ----
+    int base[A2A_MAX_WORLD];
+#pragma unroll
+    for (int d = 0; d < A2A_MAX_WORLD; ++d) base[d] = 0;
+    for (int r0 = 0; r0 < p.T; r0 += kThreads) {
+        const int t = r0 + tid;
+        const unsigned m = t < p.T ? dest_mask(p, t) : 0u;
+#pragma unroll
+        for (int d = 0; d < A2A_MAX_WORLD; ++d) {
+            const unsigned b = __ballot_sync(0xffffffffu, (m >> d) & 1u);
+            if (lane == 0) wt[warp * A2A_MAX_WORLD + d] = __popc(b);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int d = 0; d < A2A_MAX_WORLD; ++d) {
+            const unsigned b = __ballot_sync(0xffffffffu, (m >> d) & 1u);
+            int before = 0, total = 0;
+            for (int w = 0; w < kThreads / 32; ++w) {
+                const int c = wt[w * A2A_MAX_WORLD + d];
+                if (w < warp) before += c;
+                total += c;
+            }
+            if ((m >> d) & 1u) {
+                const int n = base[d] + before + __popc(b & ((1u << lane) - 1u));
+                if (n % ns == sb) list[d * per + n / ns] = (unsigned short)t;
+            }
+            base[d] += total;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+#pragma unroll
+        for (int d = 0; d < A2A_MAX_WORLD; ++d) s_cnt[d] = base[d];
+        for (int s = 0; s < kStages; ++s) mbar_init(smem_addr(bars + s), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid != 0) {
+        if (watch_kind >= 0 && warp > 0) watcher_role(p, watch_kind, watch_phase, warp - 1);
+        return;
+    }
+
+    // ---- one thread drives the copy engine ----------------------------------------------
+    const uint32_t expected = (uint32_t)ns + 1u;  // every sender block + the destination's router
+    auto arrive = [&](int d) {
+        arrive_dest(p, d, expected);
+        stamp(p, kStampDestDone + (d - p.rank + p.ws) % p.ws);
+    };
+    const int row_bytes = p.H * 2;
+    const int pieces = (row_bytes + kStageBytes - 1) / kStageBytes;
+    long long total = 0;
+    for (int i = 1; i < p.ws; ++i) {
+        const int d = (p.rank + i) % p.ws;
+        const int mine = s_cnt[d] > sb ? (s_cnt[d] - sb + ns - 1) / ns : 0;
+        if (mine == 0) arrive(d);  // nothing of ours goes there
+        total += (long long)mine * pieces;
+    }
+    constexpr int kLook = kStages / 2;
+    int g_step = 1, g_i = 0, g_piece = 0;  // generator of the next piece to load
+    auto skip_empty = [&] {
+        while (g_step < p.ws) {
+            const int d = (p.rank + g_step) % p.ws;
+            const int mine = s_cnt[d] > sb ? (s_cnt[d] - sb + ns - 1) / ns : 0;
+            if (g_i < mine) break;
+            ++g_step;
+            g_i = 0;
+        }
+    };
+    skip_empty();
+    int pend_d = -1, pend_age = 0;
+    bool failed = false;
+    for (long long q = 0; q < total + kLook && !failed; ++q) {
+        if (q < total) {
+            const int st = (int)(q % kStages);
+            if (q >= kStages) bulk_wait_read<kStages - kLook - 1>();  // the store that used this stage has read it
+            const int d = (p.rank + g_step) % p.ws;
+            const int mine = (s_cnt[d] - sb + ns - 1) / ns;
+            const int n = sb + g_i * ns;  // wire row index at the destination
+            const int t = list[d * per + g_i];
+            const int off = g_piece * kStageBytes;
+            const unsigned bytes = (unsigned)min(kStageBytes, row_bytes - off);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(p.x) + (size_t)t * row_bytes + off;
+            uint8_t* dst = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + n) * p.stage_row_bytes + off;
+            const bool last_piece = (g_piece == pieces - 1);
+            desc[st].dst = reinterpret_cast<unsigned long long>(dst);
+            desc[st].bytes = bytes;
+            desc[st].dest_done = (last_piece && g_i == mine - 1) ? d : -1;
+            mbar_expect_tx(smem_addr(bars + st), bytes);
+            bulk_load(smem_addr(ring + (size_t)st * kStageBytes), src, bytes, smem_addr(bars + st));
+            if (last_piece) {
+                g_piece = 0;
+                ++g_i;
+                skip_empty();
+            } else {
+                ++g_piece;
+            }
+        }
+        if (q >= kLook) {
+            const long long it = q - kLook;
+            const int st = (int)(it % kStages);
+            const uint32_t parity = (uint32_t)((it / kStages) & 1);
+            // the load is local and cannot be late by more than microseconds; bounded all the same
+            long long t0 = 0;
+            for (int spins = 0; !mbar_try_wait(smem_addr(bars + st), parity); ++spins) {
+                if (spins == 0) t0 = global_ns();
+                else if (global_ns() - t0 > p.timeout_ns) {
+                    record_timeout(p, kPhaseSend, -1, p.epoch);
+                    failed = true;
+                    break;
+                }
+            }
+            if (failed) break;
+            bulk_store(reinterpret_cast<void*>(desc[st].dst), smem_addr(ring + (size_t)st * kStageBytes), desc[st].bytes);
+            bulk_commit();
+            if (pend_d >= 0 && ++pend_age >= 2) {  // two more groups were committed since: the old one is through by now
+                bulk_wait_done(pend_age);
+                arrive(pend_d);
+                pend_d = -1;
+            }
+            if (desc[st].dest_done >= 0) {
+                if (pend_d >= 0) {
+                    bulk_wait_done(pend_age);
+                    arrive(pend_d);
+                }
+                pend_d = desc[st].dest_done;
+                pend_age = 0;
+            }
+        }
+    }
+    bulk_wait_done(0);  // nothing of ours is in flight when the block moves on
+    if (pend_d >= 0 && !failed) arrive(pend_d);
+}
+
+// ---------------------------------------------------------------------------
+// Router block of destination rank d (all kThreads threads).  `first` marks the one
+// router that books the pairs nobody owns (expert index out of range).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, int d, bool first, uint32_t expected) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int L = p.L, K = p.K, T = p.T;
+    const int Wc = (T + 31) >> 5;
+    unsigned* bits = reinterpret_cast<unsigned*>(smem);
+    int* wpre = reinterpret_cast<int*>(smem) + (size_t)Wc * L;
+    int* cnt = wpre + (size_t)Wc * L;
+    int* wt = cnt + L;
+    const int e0 = d * L;
+    for (int i = tid; i < Wc * L; i += kThreads) bits[i] = 0u;
+    __syncthreads();
+    for (int t = tid; t < T; t += kThreads) {
+        const int* row = p.idx + (size_t)t * K;
+        const unsigned bit = 1u << (t & 31);
+        for (int k = 0; k < K; ++k) {
+            const int e = __ldg(row + k);
+            if (e < 0 || e >= p.E) {
+                if (first) {
+                    record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+                    p.slot[(size_t)t * K + k] = -1;
+                }
+            } else if (e >= e0 && e < e0 + L) {
+                if (atomicOr(bits + (size_t)(t >> 5) * L + (e - e0), bit) & bit)  // a repeat inside the token
+                    record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+            }
+        }
+    }
+    __syncthreads();
+    for (int l = tid; l < L; l += kThreads) {
+        int run = 0;
+        for (int w = 0; w < Wc; ++w) {
+            wpre[(size_t)w * L + l] = run;
+            run += __popc(bits[(size_t)w * L + l]);
+        }
+        cnt[l] = run;
+    }
+    __syncthreads();
+    uint8_t* there = p.peer[d];
+    int* rec_tok = reinterpret_cast<int*>(there + p.off_rec_tok) + (size_t)p.rank * p.T_max;
+    unsigned* rec_ent = reinterpret_cast<unsigned*>(there + p.off_rec_ent) + (size_t)p.rank * p.T_max * K;
+    float* rec_w = reinterpret_cast<float*>(there + p.off_rec_w) + (size_t)p.rank * p.T_max * K;
+    int* meta = reinterpret_cast<int*>(there + p.off_meta);
+    int base = 0;
+    for (int r0 = 0; r0 < T; r0 += kThreads) {
+        const int t = r0 + tid;
+        bool has = false;
+        if (t < T) {
+            const int* row = p.idx + (size_t)t * K;
+            for (int k = 0; k < K; ++k) {
+                const int e = __ldg(row + k);
+                has |= (e >= e0 && e < e0 + L);
+            }
+        }
+        const unsigned b = __ballot_sync(0xffffffffu, has);
+        if (lane == 0) wt[warp] = __popc(b);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < kThreads / 32; ++w) {
+            if (w < warp) before += wt[w];
+            total += wt[w];
+        }
+        if (has) {
+            const int n = base + before + __popc(b & ((1u << lane) - 1u));  // wire row of token t at d
+            const int* row = p.idx + (size_t)t * K;
+            rec_tok[n] = t;
+            for (int k = 0; k < K; ++k) {
+                const int e = __ldg(row + k);
+                unsigned ent = kNoEntry;
+                if (e >= e0 && e < e0 + L) {
+                    bool repeat = false;
+                    for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
+                    if (!repeat) {
+                        const int l = e - e0, w = t >> 5;
+                        const int j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (t & 31)) - 1u));
+                        ent = ((unsigned)l << 16) | (unsigned)j;
+                        meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (t << 8) | k;
+                        p.slot[(size_t)t * K + k] = j;
+                    } else {
+                        p.slot[(size_t)t * K + k] = -1;
+                    }
+                }
+                rec_ent[(size_t)n * K + k] = ent;
+                rec_w[(size_t)n * K + k] = __ldg(p.w + (size_t)t * K + k);
+            }
+        }
+        base += total;
+        __syncthreads();
+    }
+    int* counts = reinterpret_cast<int*>(there + p.off_counts) + (size_t)p.rank * kMaxChunks * L;
+    for (int l = tid; l < L; l += kThreads) {
+        counts[l] = cnt[l];
+        p.send_counts[e0 + l] = cnt[l];
+    }
+    if (tid == 0) reinterpret_cast<int*>(there + p.off_hdr)[p.rank * 8] = base;
+    __syncthreads();
+    if (tid == 0) {
+        if (d == p.rank) st_release_gpu(seen_ptr(p, kFlagDispatch, p.rank), flag_value(p, 0));  // fence.gpu + store
+        else arrive_dest(p, d, expected);
+    }
+}
+
+// One 128-vector (2 KB) chunk of a wire row as four 16-byte vectors of T per lane.
+// Own rows are read from x (FP8: through the same quantise / dequantise arithmetic the wire applies).
+template <typename T, int PAYLOAD>
+__device__ __forceinline__ void load_wire_chunk(const DevParams& p, bool own, const uint8_t* src, int v0, int nvec, uint4 (&q)[4]) {
+    const int lane = threadIdx.x & 31;
+    if (PAYLOAD != A2A_PAYLOAD_FP8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * 32 + lane;
+            if (v < nvec) q[u] = own ? ld_input(reinterpret_cast<const uint4*>(src) + v) : ld_stream(reinterpret_cast<const uint4*>(src) + v);
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * 32 + lane;
+            float f[8];
+            if (own) {  // nvec % 16 == 0: the 16 lanes of a scale block are all in or all out
+                float amax = 0.f;
+                if (v < nvec) {
+                    unpack8<T>(ld_input(reinterpret_cast<const uint4*>(src) + v), f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+                }
+#pragma unroll
+                for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (v < nvec) {
+                    const float sc = amax > 0.f ? amax / 448.f : 1.f;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = f[i] / sc;
+                    unpack8_e4m3(pack8_e4m3(f), f);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] *= sc;
+                    q[u] = pack8<T>(f);
+                }
+            } else if (v < nvec) {
+                unpack8_e4m3(ld_stream(reinterpret_cast<const uint2*>(src) + v), f);
+                const float sc = ld_stream(reinterpret_cast<const float*>(src + p.H) + (v >> 4));
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] *= sc;
+                q[u] = pack8<T>(f);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Expert block `xb` of `nxb`: sources in arrival order; per source every warp of every
+// expert block takes (wire row, 2 KB chunk) items round-robin, continuing across sources
+// where the previous one left off, so no warp idles at a source boundary.
+// ---------------------------------------------------------------------------
+template <typename T, int PAYLOAD, bool PUSH>
+__device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb) {
+    __shared__ int s_ok;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int K = p.K, nvec = p.H >> 3;
+    const int nchunk = (nvec + 127) >> 7;
+    const int xw = xb * (kThreads / 32) + (tid >> 5);
+    const int nxw = nxb * (kThreads / 32);
+    const uint32_t want = flag_value(p, 0);
+    const float scale = (float)(1 + p.rank);
+    uint8_t* self = p.peer[p.rank];
+    uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
+    long long cursor = 0;
+    for (int i = 0; i < p.ws; ++i) {
+        const int s = (p.rank - i + p.ws) % p.ws;
+        if (tid == 0) s_ok = wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s) ? 1 : 0;
+        __syncthreads();
+        const int ok = s_ok;
+        __syncthreads();
+        if (!ok) return;  // timeout recorded; nothing further is published from here
+        stamp(p, kStampSourceSeen + i);
+        int n_s = ld_stream(reinterpret_cast<const int*>(self + p.off_hdr) + s * 8);
+        if (n_s < 0 || n_s > p.T_max) {
+            record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, n_s);
+            n_s = 0;
+        }
+        const int* rec_tok = reinterpret_cast<const int*>(self + p.off_rec_tok) + (size_t)s * p.T_max;
+        const unsigned* rec_ent = reinterpret_cast<const unsigned*>(self + p.off_rec_ent) + (size_t)s * p.T_max * K;
+        const float* rec_w = reinterpret_cast<const float*>(self + p.off_rec_w) + (size_t)s * p.T_max * K;
+        const bool own = (s == p.rank);
+        const long long items = (long long)n_s * nchunk;
+        for (long long it = (xw - cursor % nxw + nxw) % nxw; it < items; it += nxw) {
+            const int n = (int)(it / nchunk), v0 = (int)(it - (long long)n * nchunk) * 128;
+            const int t = ld_stream(rec_tok + n);
+            const unsigned my_ent = lane < K ? ld_stream(reinterpret_cast<const int*>(rec_ent) + (size_t)n * K + lane) : kNoEntry;
+            const float my_w = (PUSH && lane < K) ? ld_stream(rec_w + (size_t)n * K + lane) : 0.f;
+            if (t < 0 || t >= p.T_max) {
+                record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, t);
+                continue;
+            }
+            const uint8_t* src = own ? reinterpret_cast<const uint8_t*>(p.x) + (size_t)t * p.H * 2
+                                     : self + p.off_stage + ((size_t)s * p.T_max + n) * p.stage_row_bytes;
+            uint4 q[4];
+            load_wire_chunk<T, PAYLOAD>(p, own, src, v0, nvec, q);
+            float acc[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                q[u] = scale8<T>(q[u], scale);  // the placeholder expert op: T(float(row) * (1 + rank))
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+            }
+            for (int k = 0; k < K; ++k) {
+                const unsigned ent = __shfl_sync(0xffffffffu, my_ent, k);
+                const float w = __shfl_sync(0xffffffffu, my_w, k);
+                if (ent == kNoEntry) continue;
+                const int l = (int)(ent >> 16), j = (int)(ent & 0xffffu);
+                if (l >= p.L || j >= p.T_max) {
+                    record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, (int)ent);
+                    continue;
+                }
+                uint4* row = rows + (((size_t)l * p.ws + s) * p.T_max + j) * nvec;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * 32 + lane;
+                    if (v < nvec) {
+                        st_stream(row + v, q[u]);
+                        if (PUSH) {
+                            float f[8];
+                            unpack8<T>(q[u], f);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[u][e] = fmaf(f[e], w, acc[u][e]);
+                        }
+                    }
+                }
+            }
+            if (PUSH) {
+                uint4* home = reinterpret_cast<uint4*>(p.peer[s] + p.off_ret) + ((size_t)p.rank * p.T_max + t) * nvec;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * 32 + lane;
+                    if (v < nvec) st_stream(home + v, pack8<T>(acc[u]));
+                }
+            }
+        }
+        cursor += items;
+        // the block's share of source s is stored: draw a ticket, the last one tells s
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            uint32_t* ticket = p.ptickets + kPipeTicketSource * A2A_MAX_WORLD + s;
+            if (atomicAdd(ticket, 1u) == (uint32_t)nxb - 1u) {
+                *ticket = 0;
+                if (s == p.rank) {
+                    st_release_gpu(seen_ptr(p, kFlagExpert, p.rank), want);
+                } else {
+                    fence_acq_rel_sys();
+                    st_relaxed_sys(flag_ptr(p.peer[s], p.off_flags, kFlagExpert, p.rank), want);
+                }
+            }
+        }
+        stamp(p, kStampSourceDone + i);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Combine at home, PUSH: y[t] = T(sum over the ranks d holding experts of t, ascending,
+// of float(partial[d][t])).  Block `cb` of `ncb`; a warp per (token, 2 KB chunk).
+// ---------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, int ncb) {
+    __shared__ int s_ok;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int K = p.K, nvec = p.H >> 3;
+    const int nchunk = (nvec + 127) >> 7;
+    const uint32_t want = flag_value(p, 0);
+    if (tid == 0) {
+        int ok = 1;
+        for (int i = 0; i < p.ws && ok; ++i) {
+            const int d = (p.rank + i) % p.ws;
+            ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), want, p, kPhaseCombine, d) ? 1 : 0;
+        }
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;  // timeout recorded; y is left untouched
+    stamp(p, kStampExpertSeen);
+    const uint4* ret = reinterpret_cast<const uint4*>(p.peer[p.rank] + p.off_ret);
+    const long long items = (long long)p.T * nchunk;
+    const int cw = cb * (kThreads / 32) + (tid >> 5), ncw = ncb * (kThreads / 32);
+    for (long long it = cw; it < items; it += ncw) {
+        const int t = (int)(it / nchunk), v0 = (int)(it - (long long)t * nchunk) * 128;
+        unsigned bit = 0u;
+        if (lane < K) {
+            const int e = __ldg(p.idx + (size_t)t * K + lane);
+            if (e >= 0 && e < p.E) bit = 1u << (e / p.L);
+        }
+        unsigned mask = __reduce_or_sync(0xffffffffu, bit);
+        float acc[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+        while (mask) {
+            const int d = __ffs(mask) - 1;
+            mask &= mask - 1;
+            const uint4* row = ret + ((size_t)d * p.T_max + t) * nvec;
+            uint4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * 32 + lane;
+                if (v < nvec) q[u] = ld_stream(row + v);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * 32 + lane;
+                if (v < nvec) {
+                    float f[8];
+                    unpack8<T>(q[u], f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
+                }
+            }
+        }
+        uint4* y = reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * 32 + lane;
+            if (v < nvec) st_stream(y + v, pack8<T>(acc[u]));
+        }
+    }
+    __syncthreads();
+    stamp(p, kStampCombineDone);
+}
+
+// PULL combine never reads a rank it has no pair on, but a rank may only start its next call
+// once EVERY peer is through with this one's records; one thread sees to that.
+__device__ __forceinline__ void wait_all_experts(const DevParams& p) {
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+        for (int d = 0; d < p.ws; ++d)
+            if (!wait_flag_gpu(seen_ptr(p, kFlagExpert, d), flag_value(p, 0), p, kPhaseCombine, d)) break;
+}
+
+// ---------------------------------------------------------------------------
+// Kernels
+// ---------------------------------------------------------------------------
+extern __shared__ __align__(128) uint8_t a2a_pipe_smem[];
+
+// The whole path in one cooperative launch.  Blocks [0, senders) send (0 and 1 also watch),
+// the next `ws` route first, and everything from `senders` on is an expert block.
+template <typename T, int PAYLOAD, bool PUSH>
+__global__ void __launch_bounds__(kThreads, 2) pipe_forward_kernel(const __grid_constant__ DevParams p) {
+    const int G = (int)gridDim.x, b = (int)blockIdx.x;
+    const int ns = p.ws > 1 ? p.senders : 0;
+    stamp(p, kStampStart);
+    if (b < ns) {
+        stamp_value(p, kStampRole, b < 2 ? (kRoleSender | kRoleWatcher) : kRoleSender);
+        sender_role(p, a2a_pipe_smem, b, ns, b == 0 ? kFlagDispatch : (b == 1 ? kFlagExpert : -1),
+                    b == 0 ? kPhaseRecv : kPhaseCombine);
+        stamp(p, kStampSent);
+    } else {
+        const int xb = b - ns, nxb = G - ns;
+        if (xb < p.ws) {
+            router_role(p, a2a_pipe_smem, (p.rank + 1 + xb) % p.ws, xb == 0, (uint32_t)ns + 1u);
+            stamp(p, kStampSent);
+        }
+        stamp_value(p, kStampRole, xb < p.ws ? (kRoleExpert | kRoleRouter) : kRoleExpert);
+        expert_role<T, PAYLOAD, PUSH>(p, xb, nxb);
+    }
+    __syncthreads();
+    stamp(p, kStampExpertDone);
+    if (PUSH) {
+        combine_home_role<T>(p, b, G);
+    } else {
+        combine_phase<T>(p, b, G, /*own_watchers=*/false);
+        wait_all_experts(p);
+    }
+}
+
+// The same roles as separate launches, for stepping several ranks on ONE GPU (a kernel that
+// waits never shares the GPU with the kernel it waits for) and for callers that want the
+// phases apart.  ROLE 0: senders + routers.  1: one watcher block + experts.  2: one
+// watcher block + combine.
+template <typename T, int PAYLOAD, bool PUSH, int ROLE>
+__global__ void __launch_bounds__(kThreads, 2) pipe_role_kernel(const __grid_constant__ DevParams p) {
+    const int G = (int)gridDim.x, b = (int)blockIdx.x;
+    const int ns = p.ws > 1 ? p.senders : 0;
+    stamp(p, kStampStart);
+    if (ROLE == 0) {
+        if (b < ns) sender_role(p, a2a_pipe_smem, b, ns, -1, 0);
+        else router_role(p, a2a_pipe_smem, (p.rank + 1 + (b - ns)) % p.ws, b == ns, (uint32_t)ns + 1u);
+        stamp(p, kStampSent);
+    } else if (ROLE == 1) {
+        if (b == 0) watcher_role(p, kFlagDispatch, kPhaseRecv, (int)(threadIdx.x >> 5));
+        else expert_role<T, PAYLOAD, PUSH>(p, b - 1, G - 1);
+        stamp(p, kStampExpertDone);
+    } else {
+        if (b == 0) {
+            watcher_role(p, kFlagExpert, kPhaseCombine, (int)(threadIdx.x >> 5));
+        } else if (PUSH) {
+            combine_home_role<T>(p, b - 1, G - 1);
+        } else {
+            combine_phase<T>(p, b - 1, G - 1, /*own_watchers=*/false);
+        }
+        if (!PUSH) wait_all_experts(p);
+    }
+}
+
+}  // namespace a2a

@@ -19,11 +19,12 @@ from .task import MoEConfig
 
 
 class LocalWorld:
-    def __init__(self, cfg: MoEConfig, world_size: int, *, payload: str = "direct", timeout_ms: int = 2000,
-                 device: int = 0):
+    def __init__(self, cfg: MoEConfig, world_size: int, *, payload: str = "direct", schedule: str = "phased",
+                 combine: str = "pull", timeout_ms: int = 2000, device: int = 0):
         self.cfg, self.world_size = cfg, world_size
         self.ctxs: List[A2AContext] = [
-            A2AContext(cfg, r, world_size, device=device, payload=payload, timeout_ms=timeout_ms, connect=False)
+            A2AContext(cfg, r, world_size, device=device, payload=payload, schedule=schedule, combine=combine,
+                       timeout_ms=timeout_ms, connect=False)
             for r in range(world_size)
         ]
         A2AContext.attach_local(self.ctxs)
@@ -53,6 +54,15 @@ class LocalWorld:
         for c in self.ctxs:
             c.dispatch_recv_expert()
         return [c.combine(rd.weights) for c, rd in zip(self.ctxs, rank_datas)]
+
+    def forward_pipelined(self, rank_datas: Sequence) -> List[torch.Tensor]:
+        """The roles of the pipelined one-launch kernel as three launches per rank, in lock-step:
+        every rank's senders and routers, then every rank's expert blocks, then every rank's combine."""
+        for c, rd in zip(self.ctxs, rank_datas):
+            c.pipe_step(0, rd.x, rd.indices, rd.weights)
+        for c in self.ctxs:
+            c.pipe_step(1)
+        return [c.pipe_step(2) for c in self.ctxs]
 
     def check(self) -> None:
         for c in self.ctxs:

@@ -15,8 +15,7 @@ from typing import Dict, Sequence
 
 import torch
 
-NVLINK_NOMINAL_GBS = 900.0   # per direction per GPU, NVLink 5
-NVLINK_MEASURED_GBS = 770.0  # peer copy measured on this pool's B200s, per direction
+NVLINK_NOMINAL_GBS = 900.0   # per direction per GPU, NVLink 5: the peak every NVLink fraction is quoted against
 
 
 def pair_counts(indices: Sequence[torch.Tensor], num_experts: int, world_size: int):
@@ -40,7 +39,10 @@ def row_bytes(hidden_dim: int, payload: str = "direct") -> int:
 
 
 def summarize(indices: Sequence[torch.Tensor], num_experts: int, world_size: int, hidden_dim: int,
-              payload: str = "direct") -> Dict[str, float]:
+              payload: str = "direct", combine: str = "pull") -> Dict[str, float]:
+    """``algorithmic_bytes`` counts one row per (token, k) pair in both directions whatever the
+    implementation does; ``wire_bytes`` is what the chosen payload / combine mode really moves
+    (``combine="push"`` returns one partial row per (token, expert rank) instead of one per pair)."""
     pairs, rows = pair_counts(indices, num_experts, world_size)
     off = ~torch.eye(world_size, dtype=torch.bool)
     eg = (pairs * off).sum(1)
@@ -52,13 +54,13 @@ def summarize(indices: Sequence[torch.Tensor], num_experts: int, world_size: int
     row_d, row_c = row_bytes(hidden_dim, payload), 2 * hidden_dim
     alg = busiest * (row_d + row_c)  # bytes per direction on the busiest rank, dispatch + combine
     wire_dispatch_rows = busiest_d if payload in ("dedup", "fp8") else busiest
-    wire = wire_dispatch_rows * row_d + busiest * row_c
+    wire = wire_dispatch_rows * row_d + (busiest_d if combine == "push" else busiest) * row_c
     total_pairs = int(pairs.sum())
     return dict(
         busiest_rows=busiest, busiest_rows_dedup=busiest_d,
         algorithmic_bytes=alg, wire_bytes=wire,
         t_roof_us_nominal=alg / (NVLINK_NOMINAL_GBS * 1e3) if world_size > 1 else 0.0,
-        t_roof_us_measured=alg / (NVLINK_MEASURED_GBS * 1e3) if world_size > 1 else 0.0,
+        t_wire_us_nominal=wire / (NVLINK_NOMINAL_GBS * 1e3) if world_size > 1 else 0.0,
         total_pairs=total_pairs, local_pairs=int(pairs.diagonal().sum()),
     )
 

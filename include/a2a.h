@@ -48,6 +48,24 @@ enum {
     A2A_PAYLOAD_FP8 = 2     /* as DEDUP, row quantised to e4m3 with one fp32 scale per 128 values */
 };
 
+/* How the one-call forward is scheduled on the GPU. */
+enum {
+    A2A_SCHEDULE_PHASED = 0,    /* routing, sending, expert pass and combine one after the other      */
+    A2A_SCHEDULE_PIPELINED = 1  /* blocks with fixed roles (senders driving the copy engine, routers,
+                                   experts, watchers) run the phases concurrently, per peer; needs the
+                                   DEDUP payload and a device with cooperative launch                */
+};
+
+/* How expert outputs get back to the token's rank. */
+enum {
+    A2A_COMBINE_PULL = 0, /* the home rank pulls each (token, k) row from the expert's slab over NVLink
+                             and reduces the K rows with the token's weights (fp32, k ascending)       */
+    A2A_COMBINE_PUSH = 1  /* the expert rank reduces the rows of a token that IT holds with the token's
+                             weights (fp32) and pushes one partial row per (token, expert rank) home;
+                             the home rank adds the partial rows (fp32, rank ascending).  One extra
+                             rounding to the element type per partial row; pipelined schedule only.  */
+};
+
 enum { A2A_MAX_WORLD = 8, A2A_MAX_EXPERTS = 1024, A2A_MAX_TOPK = 32 };
 
 /* Problem description; the fields of the reference's MoEConfig (reference.py:10-17)
@@ -63,6 +81,11 @@ typedef struct a2a_config {
     int32_t dtype;           /* A2A_DTYPE_*: element type of x and of the output             */
     int32_t payload;         /* A2A_PAYLOAD_*                                                */
     int32_t timeout_ms;      /* budget of every device-side wait; <= 0 selects 2000 ms       */
+    int32_t schedule;        /* A2A_SCHEDULE_*                                               */
+    int32_t combine;         /* A2A_COMBINE_* (PUSH needs the pipelined schedule)            */
+    int32_t chunks;          /* phased schedule: token chunks a call is pipelined in, 1..4;
+                                0 selects 1.  Every rank of a group must pass the same value */
+    int32_t senders;         /* pipelined schedule: blocks that only move rows; 0 selects 32 */
 } a2a_config;
 
 /* First error recorded by a kernel since the last a2a_status_clear(). */
@@ -77,6 +100,11 @@ typedef struct a2a_status_t {
 
 const char* a2a_strerror(int status);
 
+/* Text describing the last A2A_ERR_CONFIG a2a_open_peers / a2a_attach_local_peers returned for
+ * this context (which rank disagreed, or how many bytes were missing).  Replaces the message of
+ * the TORCH_CHECK that guards the reference's IPC set-up (submission_v9.py:33-37, :68-75). */
+const char* a2a_last_error(a2a_ctx* ctx);
+
 /* Validate `cfg`, select the device, allocate the symmetric region and the
  * local scratch once (nothing is allocated or zeroed on the data path).
  * Replaces P2PState.__init__ + p2p_state_init (submission_v9.py:881-911, :109-131). */
@@ -87,7 +115,9 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg);
  * Replaces P2PState.close + p2p_state_destroy (submission_v9.py:913-919, :133-145). */
 int a2a_destroy(a2a_ctx* ctx);
 
-/* Size of one exported handle blob.  Replaces the fixed 64 in get_ipc_handle
+/* Size of one exported handle blob: the CUDA IPC handle followed by a fingerprint of the
+ * configuration (world size, problem sizes, element type, payload, schedule, combine mode,
+ * chunk count, size of the symmetric region).  Replaces the fixed 64 in get_ipc_handle
  * (submission_v9.py:61-66). */
 size_t a2a_ipc_handle_bytes(void);
 
@@ -96,9 +126,21 @@ size_t a2a_ipc_handle_bytes(void);
  * (one NCCL or gloo all_gather).  Replaces get_ipc_handle (submission_v9.py:61-66). */
 int a2a_export_handle(a2a_ctx* ctx, uint8_t* out);
 
-/* Map every peer's region from the gathered blobs (`world_size` blobs, rank
- * order).  Replaces open_ipc_handle per peer + heap_bases (submission_v9.py:68-75, :898-899). */
-int a2a_open_peers(a2a_ctx* ctx, const uint8_t* all_handles);
+/* The configuration fingerprint alone (the last 64 bytes of a handle blob) and the check
+ * a2a_open_peers applies to the gathered blobs, as pure host functions that need neither a
+ * context nor a device: a launcher can refuse a mismatched group before any GPU is touched.
+ * a2a_check_handles returns A2A_ERR_CONFIG and describes the problem in `msg` when `nbytes` is not
+ * world_size * a2a_ipc_handle_bytes() or when some rank's fingerprint differs from the one `cfg`
+ * gives.  No counterpart in the reference (its ranks trust each other's layout). */
+int a2a_fingerprint(const a2a_config* cfg, uint8_t* out64);
+int a2a_check_handles(const a2a_config* cfg, const uint8_t* all_handles, size_t nbytes, char* msg, size_t msg_len);
+
+/* Map every peer's region from the gathered blobs (`world_size` blobs, rank order,
+ * `nbytes` in total).  Nothing is mapped unless the byte count is right and every rank's
+ * fingerprint equals this rank's: a truncated gather or a rank created with another payload,
+ * schedule or problem size returns A2A_ERR_CONFIG (details: a2a_last_error).  Replaces
+ * open_ipc_handle per peer + heap_bases (submission_v9.py:68-75, :898-899). */
+int a2a_open_peers(a2a_ctx* ctx, const uint8_t* all_handles, size_t nbytes);
 
 /* Same-process alternative to the two calls above: `peers[r]` is rank r's
  * context living in this process (on this or another GPU).  No counterpart in
@@ -165,10 +207,27 @@ int a2a_set_fused(a2a_ctx* ctx, int on);
 int a2a_forward_host(a2a_ctx* ctx, const void* x_host, const int32_t* topk_idx_host,
                      const float* topk_weights_host, void* y_host, int num_tokens, void* stream);
 
+/* The roles of the pipelined one-launch kernel as three separate launches (same device code):
+ * role 0 = senders + routers (takes x, topk_idx, topk_weights and num_tokens; starts the call),
+ * role 1 = dispatch watchers + expert blocks, role 2 = expert-flag watchers + combine (takes y).
+ * Arguments a role does not use may be NULL / 0.  For stepping several ranks on one GPU -- a
+ * kernel that waits for a peer never shares a GPU with the kernel it waits for -- and for
+ * timing the roles apart.  Needs a context created with A2A_SCHEDULE_PIPELINED.  The reference
+ * splits its fused call the same way into dispatch and combine ops (submission_v9.py:675-731). */
+int a2a_pipe_step(a2a_ctx* ctx, int role, const void* x, const int32_t* topk_idx, const float* topk_weights,
+                  void* y, int num_tokens, void* stream);
+
 /* Cross-GPU rendezvous on the device: returns (on the stream) once every rank's
  * stream has reached it.  Bounded wait.  Used to align ranks before timing.
  * Plays the role of dist.barrier() around the timed call (my_eval.py:160-172). */
 int a2a_barrier(a2a_ctx* ctx, void* stream);
+
+/* Measurement helper: one asynchronous copy of `bytes` from this rank's slab rows into rank
+ * `peer`'s slab rows (both dead between calls), on `stream`.  Timed with events while every
+ * rank copies to its neighbour it gives the per-direction peer-copy bandwidth of the box, the
+ * measured figure NVLink fractions can be read against.  `bytes` must not exceed the slab
+ * region.  The reference quotes its link figures from vendor numbers instead (README.md:28-29). */
+int a2a_link_probe(a2a_ctx* ctx, int peer, size_t bytes, void* stream);
 
 /* Test/inspection helper: copy what PyTorchAllToAll.dispatch returns
  * (reference.py:148) into caller-provided device buffers:
@@ -203,21 +262,33 @@ int a2a_copy_route(a2a_ctx* ctx, int32_t* slots_out, int32_t* send_counts_out, v
  * 4096, experts_per_token <= 32 -- larger requests return A2A_ERR_CONFIG and enqueue
  * nothing.  The first call on a device resolves the array's device address: make it
  * before any stream capture.  All calls on a device share the array (the kernel clears
- * what it uses); calls whose kernels overlap on the GPU race -- keep them ordered. */
+ * what it uses); calls whose kernels overlap on the GPU race -- keep them ordered.  Unlike
+ * a2a_route there is no status word: a pair whose expert index is out of range or repeats an
+ * earlier expert of its token is dropped silently -- its slot is -1 and nothing else reports it. */
 int a2a_route_noalloc(const int32_t* topk_idx, int num_tokens, int num_experts, int experts_per_token,
                       int32_t* slots_out, int32_t* send_counts_out, void* stream);
 
-/* Read (and optionally clear) the first error recorded by a kernel.  Waits for
- * nothing: reads what is there now. */
+/* Read the first error recorded by a kernel since the last a2a_status_clear.  Waits for
+ * nothing on the caller's streams: reads what is there now. */
 int a2a_status(a2a_ctx* ctx, a2a_status_t* out);
+/* Forget the recorded error and re-arm the block-arrival counters a cut-short kernel may have
+ * left half counted.  REQUIRED after A2A_ERR_TIMEOUT before the context is used again: while a
+ * timeout is recorded every wait of every later kernel gives up at once.  Synchronises the device. */
 int a2a_status_clear(a2a_ctx* ctx);
+/* The code a2a_status would report, read from a word in mapped host memory that the kernels
+ * mirror it into: no CUDA call, no synchronisation -- cheap enough to look at before every
+ * call (the plugin entry does).  May lag a kernel that is still running.  Plays the role of
+ * the exception a failed TORCH_CHECK raises in the reference (submission_v9.py:33-37). */
+int a2a_status_peek(a2a_ctx* ctx);
 
 /* In-kernel trace.  While enabled, thread 0 of every block stamps the SM cycle counter
  * at each phase boundary of the launches that follow (slot 0 of a block holds the
- * nanosecond global timer at its start; then start, routed, sent, dispatch-seen,
- * expert-done, expert-seen, combine-done).  a2a_trace_read synchronises the device and copies the
- * stamps of the most recent traced launch to host memory: `out` must hold
- * max_blocks * 8 int64.  Both calls synchronise: keep them
+ * nanosecond global timer at its start; then start, routed (pipelined: the block's role bits),
+ * sent, dispatch-seen, expert-done, expert-seen, combine-done; the pipelined kernel also fills
+ * slots 8+i / 16+i with "rows of the i-th source seen / done" and 24+i with "i-th destination
+ * finished").  a2a_trace_read synchronises the device and copies the stamps of the most recent
+ * traced launch to host memory: `out` must hold max_blocks * 32 int64 (*stamps_per_block
+ * returns the 32).  Both calls synchronise: keep them
  * off the timed path.  Replaces the profile buffer of the final reference submission
  * (submission_v9.py:117, :162-184, p2p_state_get_profile). */
 int a2a_trace_enable(a2a_ctx* ctx, int on);

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_strerror_and_handle_size():
     lib = _lib.load()
-    assert lib.a2a_ipc_handle_bytes() == 64
+    assert lib.a2a_ipc_handle_bytes() == 128  # 64-byte CUDA IPC handle + configuration fingerprint
     assert _lib.strerror(0) == "ok"
     for code in range(1, 6):
         assert _lib.strerror(code) not in ("ok", "unknown status")
@@ -40,6 +40,11 @@ def test_strerror_and_handle_size():
     dict(world_size=0), dict(world_size=9), dict(rank=2), dict(num_experts=7), dict(num_experts=2048),
     dict(experts_per_token=0), dict(experts_per_token=33), dict(hidden_dim=100), dict(hidden_dim=0),
     dict(max_num_tokens=0), dict(dtype=5), dict(payload=7), dict(device=-1),
+    dict(schedule=2), dict(combine=3), dict(chunks=9), dict(senders=-1),
+    dict(schedule=1, payload=0),            # the pipelined schedule moves (token, rank) wire rows: needs DEDUP
+    dict(schedule=0, payload=1, combine=1),  # expert-side reduction exists in the pipelined schedule only
+    dict(schedule=1, payload=1, chunks=2),
+    dict(schedule=1, payload=1, senders=1),  # two sender blocks carry the watchers
 ])
 def test_bad_config_is_rejected_without_a_device(kw):
     lib = _lib.load()

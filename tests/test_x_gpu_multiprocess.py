@@ -17,20 +17,26 @@ from parity import quantised_inputs
 
 pytestmark = pytest.mark.gpu
 
-# (E, K, H, T, seed, back-to-back calls, payload)
+# (E, K, H, T, seed, back-to-back calls, payload, schedule, combine)
 CASES = [
-    (8, 2, 2048, 16, 0, 4, "direct"),
-    (64, 6, 2048, 64, 2, 30, "direct"),
-    (256, 8, 7168, 256, 3, 20, "direct"),
-    (64, 6, 2048, 64, 2, 30, "dedup"),
-    (256, 8, 7168, 256, 3, 20, "dedup"),
-    (256, 8, 7168, 256, 4, 20, "fp8"),
+    (8, 2, 2048, 16, 0, 4, "direct", "phased", "pull"),
+    (64, 6, 2048, 64, 2, 30, "direct", "phased", "pull"),
+    (256, 8, 7168, 256, 3, 20, "direct", "phased", "pull"),
+    # many items per block and strongly different token counts per rank: a combine block that got ahead
+    # of this rank's own routing would read a stale slot
+    (64, 6, 2048, 1024, 7, 12, "direct", "phased", "pull"),
+    (256, 8, 7168, 256, 3, 20, "dedup", "phased", "pull"),
+    (256, 8, 7168, 256, 4, 20, "fp8", "phased", "pull"),
+    (64, 6, 2048, 64, 2, 30, "dedup", "pipelined", "push"),
+    (256, 8, 7168, 256, 3, 20, "dedup", "pipelined", "push"),
+    (256, 8, 7168, 256, 3, 20, "dedup", "pipelined", "pull"),
+    (64, 6, 2048, 1024, 7, 12, "dedup", "pipelined", "push"),
 ]
 
 
 def _prepare(ws, tmp):
     """Two alternating input sets per case; expectation per rank from the CPU checker."""
-    for ci, (E, K, H, T, seed, _, payload) in enumerate(CASES):
+    for ci, (E, K, H, T, seed, _, payload, _, _) in enumerate(CASES):
         for si, sd in enumerate((seed, seed + 1000)):
             datas = [pkg.generate_input(E, K, H, T, seed=sd, rank=r, world_size=ws, ragged=True) for r in range(ws)]
             cfg = datas[0][0]
@@ -61,7 +67,7 @@ def _worker(rank, ws, port, tmp, q):
     dist.init_process_group("nccl", rank=rank, world_size=ws, device_id=torch.device(f"cuda:{rank}"))
     ok, msg = True, ""
     try:
-        for ci, (E, K, H, T, seed, iters, payload) in enumerate(CASES):
+        for ci, (E, K, H, T, seed, iters, payload, schedule, combine) in enumerate(CASES):
             cfg = pkg.MoEConfig(E, K, H, T)
             sets = []
             for si in range(2):
@@ -76,14 +82,15 @@ def _worker(rank, ws, port, tmp, q):
             dist.barrier()
             outs = []
             for i in range(iters):  # back to back, no host sync: epochs and slab reuse under real concurrency
-                outs.append(custom_kernel((cfg, sets[i % 2][0], rank, ws), payload=payload))
+                outs.append(custom_kernel((cfg, sets[i % 2][0], rank, ws), payload=payload, schedule=schedule,
+                                          combine=combine))
             torch.cuda.synchronize()
             for ctx in _CONTEXTS.values():
                 ctx.check()
             # alternating inputs: a flag that overtook its data would hand a consumer the other set's rows
             for i in range(2, iters):
                 if not torch.equal(outs[i].view(torch.int16), outs[i - 2].view(torch.int16)):
-                    ok, msg = False, f"case {ci} {payload}: call {i} differs from call {i - 2}"
+                    ok, msg = False, f"case {ci} {payload}/{schedule}/{combine}: call {i} differs from call {i - 2}"
             for i in (0, 1):
                 _, y, y_q = sets[i]
                 got = outs[i].cpu()
@@ -96,7 +103,7 @@ def _worker(rank, ws, port, tmp, q):
                 else:
                     good = float(_within(got, y, 2e-2).max()) <= 1
                 if not good:
-                    ok, msg = False, f"case {ci} {payload}: output of call {i} outside tolerance"
+                    ok, msg = False, f"case {ci} {payload}/{schedule}/{combine}: output of call {i} outside tolerance"
             if not ok:
                 break
             dist.barrier()
@@ -122,7 +129,7 @@ def test_custom_kernel_over_ipc(ws):
         procs = [ctx.Process(target=_worker, args=(r, ws, 29800 + ws, tmp, q), daemon=True) for r in range(ws)]
         for p in procs:
             p.start()
-        res = [q.get(timeout=180) for _ in range(ws)]
+        res = [q.get(timeout=300) for _ in range(ws)]
         for p in procs:
             p.join(30)
     bad = [r for r in res if not r[1]]

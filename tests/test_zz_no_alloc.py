@@ -55,6 +55,37 @@ def test_no_alloc_routing_matches_context_routing_twice_in_a_row():
         ctx.close()
 
 
+def test_no_alloc_routing_at_its_limits_and_with_no_tokens():
+    """The largest request the static tables take (4096 tokens, 1024 experts, top-32: several tokens
+    per thread, 128 bitmap words per expert, the far end of the array in use) and an empty one, each
+    after a smaller call that left its bits behind; checked against the CPU routing of the checker."""
+    from oracle import a2a_oracle as O
+
+    torch.cuda.set_device(0)
+    g = torch.Generator().manual_seed(7)
+    small = torch.stack([torch.randperm(64, generator=g)[:4] for _ in range(100)]).to(torch.int32)
+    rc, _, _ = _route_noalloc(small.to(DEV), 64, 4)
+    assert rc == 0
+    E, K, T = 1024, 32, 4096
+    big = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    rc, slots, counts = _route_noalloc(big.to(DEV), E, K)
+    assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    want_slots, want_counts = O.route_tables(big, E)
+    assert torch.equal(slots.cpu(), want_slots) and torch.equal(counts.cpu(), want_counts)
+    # no tokens at all, right after the dense call: every count is zero, nothing else is written
+    empty = torch.zeros(0, 8, dtype=torch.int32, device=DEV)
+    rc, slots, counts = _route_noalloc(empty, 256, 8)
+    assert rc == 0, _lib.strerror(rc)
+    torch.cuda.synchronize()
+    assert slots.numel() == 0 and torch.equal(counts.cpu(), torch.zeros(256, dtype=torch.int32))
+    # and a normal call after that is undisturbed
+    rc, slots, counts = _route_noalloc(small.to(DEV), 64, 4)
+    torch.cuda.synchronize()
+    want_slots, want_counts = O.route_tables(small, 64)
+    assert rc == 0 and torch.equal(slots.cpu(), want_slots) and torch.equal(counts.cpu(), want_counts)
+
+
 def test_no_alloc_routing_rejects_sizes_beyond_its_static_tables():
     torch.cuda.set_device(0)
     idx = torch.zeros(4, 2, dtype=torch.int32, device=DEV)
