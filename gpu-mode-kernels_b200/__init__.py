@@ -6,6 +6,8 @@ Public surface (mirrors the reference task, amd-distributed/all2all):
   (reference.py:10-51, :237-253).
 * ``custom_kernel(data)`` -- the plugin entry point (task.py:8-9); runs the
   hand-written sm_100a kernels through the C-ABI library ``liba2a.so``.
+* ``check_implementation(data, output, reference_output)`` -- the task's checker
+  (reference.py:275-283) for harnesses; import it from ``.all2all``.
 * ``A2AContext`` -- per-process-group state: symmetric receive buffers, peer
   mappings, flags (the role ``P2PState`` plays in submission_v9.py:880-947).
 

@@ -46,7 +46,7 @@ constexpr int kFlagStride = 32;  // uint32 words between two flags = 128 bytes
 constexpr int kFp8Block = 128;   // elements sharing one fp32 scale
 constexpr int kMaxChunks = 4;    // token chunks a call is pipelined in (whole 32-token bitmap words each)
 constexpr int kStageBytes = 16384;  // one stage of a sender block's shared-memory ring (a row piece)
-constexpr int kStages = 4;          // stages of that ring: two bulk loads and two bulk stores in flight
+constexpr int kStages = 6;          // stages of that ring: four bulk loads and two bulk stores in flight
 constexpr unsigned kNoEntry = 0xffffffffu;  // record entry of a (token, k) pair that has no row on the destination
 enum FlagKind : int { kFlagDispatch = 0, kFlagExpert = 1, kFlagBarrier = 2, kNumFlagKinds = 3 };
 enum Phase : int { kPhaseRoute = 1, kPhaseSend = 2, kPhaseRecv = 3, kPhaseExpert = 4, kPhaseCombine = 5, kPhaseBarrier = 6 };

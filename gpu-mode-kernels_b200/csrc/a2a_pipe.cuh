@@ -5,7 +5,7 @@
 //   senders  (p.senders blocks; one thread each drives the SM's copy engine)
 //            For destination rank d = rank+1, rank+2, ... (a ring: at any moment every
 //            rank sends to a different peer) the token rows wanted by d are bulk-loaded
-//            from HBM into a four-stage shared-memory ring and bulk-stored straight into
+//            from HBM into a six-stage shared-memory ring and bulk-stored straight into
 //            d's stage buffer, one wire row per (token, destination).  No routing table is
 //            needed for that, so rows move from the first microsecond.  When a
 //            destination's last store has completed the block draws a ticket; the last
@@ -170,7 +170,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
         if (mine == 0) arrive(d);  // nothing of ours goes there
         total += (long long)mine * pieces;
     }
-    constexpr int kLook = kStages / 2;
+    constexpr int kLook = kStages - 2;  // loads issued ahead of the store that follows them
     int g_step = 1, g_i = 0, g_piece = 0;  // generator of the next piece to load
     auto skip_empty = [&] {
         while (g_step < p.ws) {
@@ -264,16 +264,23 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
     for (int t = tid; t < T; t += kThreads) {
         const int* row = p.idx + (size_t)t * K;
         const unsigned bit = 1u << (t & 31);
-        for (int k = 0; k < K; ++k) {
-            const int e = __ldg(row + k);
-            if (e < 0 || e >= p.E) {
-                if (first) {
-                    record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
-                    p.slot[(size_t)t * K + k] = -1;
+        for (int k0 = 0; k0 < K; k0 += 8) {
+            int e8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) e8[u] = (k0 + u < K) ? __ldg(row + k0 + u) : e0;  // loaded together
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int k = k0 + u, e = e8[u];
+                if (k >= K) break;
+                if (e < 0 || e >= p.E) {
+                    if (first) {
+                        record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+                        p.slot[(size_t)t * K + k] = -1;
+                    }
+                } else if (e >= e0 && e < e0 + L) {
+                    if (atomicOr(bits + (size_t)(t >> 5) * L + (e - e0), bit) & bit)  // a repeat inside the token
+                        record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
                 }
-            } else if (e >= e0 && e < e0 + L) {
-                if (atomicOr(bits + (size_t)(t >> 5) * L + (e - e0), bit) & bit)  // a repeat inside the token
-                    record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
             }
         }
     }
@@ -314,25 +321,39 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
         if (has) {
             const int n = base + before + __popc(b & ((1u << lane) - 1u));  // wire row of token t at d
             const int* row = p.idx + (size_t)t * K;
+            const float* wrow = p.w + (size_t)t * K;
             rec_tok[n] = t;
-            for (int k = 0; k < K; ++k) {
-                const int e = __ldg(row + k);
-                unsigned ent = kNoEntry;
-                if (e >= e0 && e < e0 + L) {
-                    bool repeat = false;
-                    for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
-                    if (!repeat) {
-                        const int l = e - e0, w = t >> 5;
-                        const int j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (t & 31)) - 1u));
-                        ent = ((unsigned)l << 16) | (unsigned)j;
-                        meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (t << 8) | k;
-                        p.slot[(size_t)t * K + k] = j;
-                    } else {
-                        p.slot[(size_t)t * K + k] = -1;
-                    }
+            // eight pairs at a time: their indices and weights are loaded together (one memory latency,
+            // not one per pair) before anything is stored
+            for (int k0 = 0; k0 < K; k0 += 8) {
+                int e8[8];
+                float w8[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    e8[u] = (k0 + u < K) ? __ldg(row + k0 + u) : -1;
+                    w8[u] = (k0 + u < K) ? __ldg(wrow + k0 + u) : 0.f;
                 }
-                rec_ent[(size_t)n * K + k] = ent;
-                rec_w[(size_t)n * K + k] = __ldg(p.w + (size_t)t * K + k);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int k = k0 + u, e = e8[u];
+                    if (k >= K) break;
+                    unsigned ent = kNoEntry;
+                    if (e >= e0 && e < e0 + L) {
+                        bool repeat = false;
+                        for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
+                        if (!repeat) {
+                            const int l = e - e0, w = t >> 5;
+                            const int j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (t & 31)) - 1u));
+                            ent = ((unsigned)l << 16) | (unsigned)j;
+                            meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (t << 8) | k;
+                            p.slot[(size_t)t * K + k] = j;
+                        } else {
+                            p.slot[(size_t)t * K + k] = -1;
+                        }
+                    }
+                    rec_ent[(size_t)n * K + k] = ent;
+                    rec_w[(size_t)n * K + k] = w8[u];
+                }
             }
         }
         base += total;
