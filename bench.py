@@ -283,7 +283,7 @@ def main():
 
     wl = pkg.WORKLOADS[args.workload]
     payload = args.payload or wl.get("payload", "dedup")
-    schedule = args.schedule or ("pipelined" if payload == "dedup" else "phased")
+    schedule = args.schedule or ("pipelined" if payload in ("dedup", "fp8") else "phased")
     combine = args.combine or ("push" if schedule == "pipelined" else "pull")
     cfg, rd_cpu, _, _ = pkg.workload_input(args.workload, rank, ws)
     rd = rd_cpu.to(dev)

@@ -324,7 +324,7 @@ def _device_view(ptr: int, shape, dtype: torch.dtype, device_index: int) -> torc
 # ---------------------------------------------------------------------------
 _CONTEXTS: Dict[tuple, A2AContext] = {}
 DEFAULT_PAYLOAD = "dedup"  # one wire row per (token, destination rank): least NVLink traffic, same results
-# "auto": the pipelined one-launch kernel where the configuration allows it (DEDUP payload, shared-memory
+# "auto": the pipelined one-launch kernel where the configuration allows it (DEDUP / FP8 payload, shared-memory
 # limits), else the phased one.  The decision depends on the configuration only, so every rank takes the same.
 DEFAULT_SCHEDULE = os.environ.get("A2A_SCHEDULE", "auto")
 DEFAULT_COMBINE = os.environ.get("A2A_COMBINE", "push")  # used with the pipelined schedule; phased is always pull
@@ -338,7 +338,7 @@ def _context_for(cfg: MoEConfig, rank: int, world_size: int, device_index: int, 
     if ctx is None:
         # first call with this shape: collective set-up (every rank gets here in the same call)
         ctx = None
-        if schedule in ("auto", "pipelined") and (payload == "dedup" or schedule == "pipelined"):
+        if schedule in ("auto", "pipelined") and (payload in ("dedup", "fp8") or schedule == "pipelined"):
             try:
                 ctx = A2AContext(cfg, rank, world_size, device=device_index, payload=payload,
                                  schedule="pipelined", combine=combine)

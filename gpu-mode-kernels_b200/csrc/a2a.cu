@@ -164,8 +164,13 @@ int check_blobs(const a2a_config& cfg, const uint8_t* all, size_t nbytes, char* 
     return A2A_OK;
 }
 
-// Sender blocks of the pipelined kernel: 32 keep about 2 MB on the way to the peers.
-int pipe_senders(const a2a_config& c) { return c.world_size > 1 ? (c.senders > 0 ? c.senders : 32) : 0; }
+// Sender blocks of the pipelined kernel.  16-bit payload: one thread per block drives the copy
+// engine, 32 blocks keep about 2 MB on the way to the peers.  FP8: every warp quantises a row of
+// its own, 64 blocks = 512 rows in the making.
+int pipe_senders(const a2a_config& c) {
+    if (c.world_size == 1) return 0;
+    return c.senders > 0 ? c.senders : (c.payload == A2A_PAYLOAD_FP8 ? 64 : 32);
+}
 
 int validate(const a2a_config& c) {
     if (c.world_size < 1 || c.world_size > A2A_MAX_WORLD) return A2A_ERR_CONFIG;
@@ -188,7 +193,9 @@ int validate(const a2a_config& c) {
     if (c.combine == A2A_COMBINE_PUSH && c.schedule != A2A_SCHEDULE_PIPELINED) return A2A_ERR_CONFIG;
     if (c.schedule == A2A_SCHEDULE_PIPELINED) {
         // the senders move one wire row per (token, destination): the per-pair DIRECT payload has none
-        if (c.payload != A2A_PAYLOAD_DEDUP) return A2A_ERR_CONFIG;
+        if (c.payload != A2A_PAYLOAD_DEDUP && c.payload != A2A_PAYLOAD_FP8) return A2A_ERR_CONFIG;
+        // FP8: a warp assembles a whole wire row in its own stage of the sender ring
+        if (c.payload == A2A_PAYLOAD_FP8 && make_layout(c).stage_row_bytes > kWarpStageBytes) return A2A_ERR_CONFIG;
         if (c.chunks > 1) return A2A_ERR_CONFIG;
         const int senders = pipe_senders(c);
         if (c.world_size > 1 && senders < 2) return A2A_ERR_CONFIG;  // blocks 0 and 1 carry the watchers
@@ -243,20 +250,25 @@ template <typename T, int P> struct ExpertSel {
         return expert_kernel<T, P, false, false, false, true>;                                           // expert_done
     }
 };
-// pipelined schedule: (element type, push/pull) -> kernel; role -1 = the one-launch kernel
-template <typename T, bool PUSH>
+// pipelined schedule: (element type, payload, push/pull) -> kernel; role -1 = the one-launch kernel
+template <typename T, int P, bool PUSH>
 KernelFn pipe_fn_tp(int role) {
     switch (role) {
-        case 0: return pipe_role_kernel<T, A2A_PAYLOAD_DEDUP, PUSH, 0>;
-        case 1: return pipe_role_kernel<T, A2A_PAYLOAD_DEDUP, PUSH, 1>;
-        case 2: return pipe_role_kernel<T, A2A_PAYLOAD_DEDUP, PUSH, 2>;
-        default: return pipe_forward_kernel<T, A2A_PAYLOAD_DEDUP, PUSH>;
+        case 0: return pipe_role_kernel<T, P, PUSH, 0>;
+        case 1: return pipe_role_kernel<T, P, PUSH, 1>;
+        case 2: return pipe_role_kernel<T, P, PUSH, 2>;
+        default: return pipe_forward_kernel<T, P, PUSH>;
     }
 }
-KernelFn pipe_fn(const a2a_ctx* c, int role) {
+template <typename T>
+KernelFn pipe_fn_t(const a2a_ctx* c, int role) {
     const bool push = c->cfg.combine == A2A_COMBINE_PUSH;
-    if (c->cfg.dtype == A2A_DTYPE_BF16) return push ? pipe_fn_tp<__nv_bfloat16, true>(role) : pipe_fn_tp<__nv_bfloat16, false>(role);
-    return push ? pipe_fn_tp<__half, true>(role) : pipe_fn_tp<__half, false>(role);
+    if (c->cfg.payload == A2A_PAYLOAD_FP8)
+        return push ? pipe_fn_tp<T, A2A_PAYLOAD_FP8, true>(role) : pipe_fn_tp<T, A2A_PAYLOAD_FP8, false>(role);
+    return push ? pipe_fn_tp<T, A2A_PAYLOAD_DEDUP, true>(role) : pipe_fn_tp<T, A2A_PAYLOAD_DEDUP, false>(role);
+}
+KernelFn pipe_fn(const a2a_ctx* c, int role) {
+    return c->cfg.dtype == A2A_DTYPE_BF16 ? pipe_fn_t<__nv_bfloat16>(c, role) : pipe_fn_t<__half>(c, role);
 }
 
 KernelFn combine_fn(const a2a_ctx* c) {
@@ -428,6 +440,14 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     p.off_hdr = c->lay.off_hdr; p.off_ret = c->lay.off_ret;
     p.stage_row_bytes = c->lay.stage_row_bytes;
     p.senders = pipe_senders(c->cfg);
+    {
+        // router blocks per destination: about 32 in all, never more than there are 32-token words
+        const int words = (T + 31) / 32;
+        int r = 32 / cfg->world_size;
+        if (r > 8) r = 8;
+        if (r > words) r = words;
+        p.routers = r < 1 ? 1 : r;
+    }
     p.rank = cfg->rank; p.ws = cfg->world_size; p.E = E; p.K = K; p.H = H; p.T_max = T; p.L = L;
     p.timeout_ns = (long long)c->cfg.timeout_ms * 1000000LL;
     {
@@ -480,7 +500,8 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
             c->fused = true;
             // the one launch needs every block resident and room for the roles: senders, one router per
             // destination, and at least as many expert blocks again
-            if (coop == 0 || c->forward_grid < p.senders + 2 * cfg->world_size) {
+            const int watchers = (cfg->payload == A2A_PAYLOAD_FP8 && cfg->world_size > 1) ? 2 : 0;
+            if (coop == 0 || c->forward_grid < watchers + p.senders + 2 * cfg->world_size * p.routers) {
                 a2a_destroy(c);
                 return A2A_ERR_CONFIG;
             }
@@ -684,7 +705,7 @@ int a2a_pipe_step(a2a_ctx* c, int role, const void* x, const int32_t* idx, const
         if (!rows_aligned(x) || reinterpret_cast<uintptr_t>(w) % 4 != 0) return A2A_ERR_CONFIG;
         c->p.x = x;
         c->p.w = w;
-        r = launch(c, pipe_fn(c, 0), c->p.senders + ws, c->pipe_smem, st);
+        r = launch(c, pipe_fn(c, 0), c->p.senders + ws * c->p.routers, c->pipe_smem, st);
         if (r == A2A_OK) c->sent = true;
         return r;
     }

@@ -82,6 +82,7 @@ struct DevParams {
     size_t off_ret;         // [ws][T_max][H] elements: partial sums pushed home by expert rank d (PUSH combine)
     int stage_row_bytes;
     int senders;            // blocks of the pipelined kernel that only move rows to the peers
+    int routers;            // router blocks per destination rank (each writes the records of a slice of the tokens)
     int rank, ws, E, K, H, T_max, L;
     int T;                  // tokens of this rank in the current call
     int chunks;             // token chunks per call, 1..kMaxChunks (same on every rank)
@@ -114,6 +115,19 @@ __device__ __forceinline__ void stamp(const DevParams& p, int which) {
         p.trace[(size_t)blockIdx.x * kNumStamps + which] = clock64();
         if (which == kStampStart) p.trace[(size_t)blockIdx.x * kNumStamps + kStampGlobalNs] = global_ns();
     }
+}
+
+// Stamp by whichever thread the caller elects (exactly one per block and slot).
+__device__ __forceinline__ void stamp_by(const DevParams& p, int which, bool elected) {
+    if (p.trace != nullptr && elected) p.trace[(size_t)blockIdx.x * kNumStamps + which] = clock64();
+}
+
+// Named barriers (ids 1..15; 0 is __syncthreads): `count` threads take part, arrivals do not wait.
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // Value stamp (not a time): e.g. the role of the block.

@@ -10,7 +10,7 @@
 //            needed for that, so rows move from the first microsecond.  When a
 //            destination's last store has completed the block draws a ticket; the last
 //            ticket (all senders + that destination's router) publishes the dispatch flag.
-//   routers  (one block per destination, then they join the experts)
+//   routers  (a few blocks per destination, then they join the experts)
 //            build the [token x expert] bitmap of the destination's experts only, derive
 //            the slot of every (token, k) row by popc, and write the destination its
 //            records: per wire row the token, the (local expert, slot) of each pair and the
@@ -74,7 +74,8 @@ __device__ __forceinline__ unsigned dest_mask(const DevParams& p, int t) {
 }
 
 // One arrival of a sender thread or a router block on destination d's ticket; the last of
-// the `expected` arrivals publishes this rank's dispatch flag on d.  Called by ONE thread
+// the `expected` arrivals publishes this rank's dispatch flag on d (for d = this rank: the
+// local word the expert blocks wait on; only the routers arrive there).  Called by ONE thread
 // whose own stores (and, through a barrier, its block's) are complete.
 __device__ __forceinline__ void arrive_dest(const DevParams& p, int d, uint32_t expected) {
     fence_async_global();  // bulk stores of this thread, completed above, before the ordinary fence
@@ -82,8 +83,12 @@ __device__ __forceinline__ void arrive_dest(const DevParams& p, int d, uint32_t 
     uint32_t* ticket = p.ptickets + kPipeTicketDest * A2A_MAX_WORLD + d;
     if (atomicAdd(ticket, 1u) == expected - 1) {
         *ticket = 0;  // everyone has arrived: re-arm for the next call
-        fence_acq_rel_sys();
-        st_relaxed_sys(flag_ptr(p.peer[d], p.off_flags, kFlagDispatch, p.rank), flag_value(p, 0));
+        if (d == p.rank) {
+            st_release_gpu(seen_ptr(p, kFlagDispatch, p.rank), flag_value(p, 0));
+        } else {
+            fence_acq_rel_sys();
+            st_relaxed_sys(flag_ptr(p.peer[d], p.off_flags, kFlagDispatch, p.rank), flag_value(p, 0));
+        }
     }
 }
 
@@ -98,46 +103,56 @@ __device__ __forceinline__ void watcher_role(const DevParams& p, int kind, int p
 }
 
 // ---------------------------------------------------------------------------
-// Sender block `sb` of `ns`.  All threads build the block's token lists; then thread 0
-// drives the copy engine while, if `watch_kind` >= 0, warps 1.. watch the peers' flags of
-// that kind (they start only after the set-up barrier: a watcher may wait for a long time).
+// Sender blocks.  Shared-memory layout: ring | mbarriers | descriptors | token lists | warp totals.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, int sb, int ns, int watch_kind,
-                                            int watch_phase) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int per = pipe_list_per(p.T_max, ns);
-    uint8_t* ring = smem;
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (size_t)kStages * kStageBytes);
-    SendDesc* desc = reinterpret_cast<SendDesc*>(smem + (size_t)kStages * kStageBytes + 128);
-    unsigned short* list = reinterpret_cast<unsigned short*>(desc + 2 * kStages);
-    int* wt = reinterpret_cast<int*>(smem + pipe_sender_smem(p.T_max, p.ws, ns) - 8 * A2A_MAX_WORLD * 4);
-    __shared__ int s_cnt[A2A_MAX_WORLD];
+struct SenderSmem {
+    uint8_t* ring;
+    unsigned long long* bars;
+    SendDesc* desc;
+    unsigned short* list;  // [ws][per]: this block's share of every destination's token list
+    int* wt;
+    int per;
+};
 
-    // ---- this block's share of every destination's token list (ballot / popc compaction) ----
+__device__ __forceinline__ SenderSmem carve_sender(const DevParams& p, uint8_t* smem, int ns) {
+    SenderSmem m;
+    m.per = pipe_list_per(p.T_max, ns);
+    m.ring = smem;
+    m.bars = reinterpret_cast<unsigned long long*>(smem + (size_t)kStages * kStageBytes);
+    m.desc = reinterpret_cast<SendDesc*>(smem + (size_t)kStages * kStageBytes + 128);
+    m.list = reinterpret_cast<unsigned short*>(m.desc + 2 * kStages);
+    m.wt = reinterpret_cast<int*>(smem + pipe_sender_smem(p.T_max, p.ws, ns) - 8 * A2A_MAX_WORLD * 4);
+    return m;
+}
+
+// All threads: this block's share (wire rows n with n % ns == sb) of every destination's token
+// list by ballot / popc compaction, and the total number of wire rows per destination in cnt[].
+__device__ __forceinline__ void build_send_lists(const DevParams& p, const SenderSmem& m, int sb, int ns, int* cnt) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int base[A2A_MAX_WORLD];
 #pragma unroll
     for (int d = 0; d < A2A_MAX_WORLD; ++d) base[d] = 0;
     for (int r0 = 0; r0 < p.T; r0 += kThreads) {
         const int t = r0 + tid;
-        const unsigned m = t < p.T ? dest_mask(p, t) : 0u;
+        const unsigned mask = t < p.T ? dest_mask(p, t) : 0u;
 #pragma unroll
         for (int d = 0; d < A2A_MAX_WORLD; ++d) {
-            const unsigned b = __ballot_sync(0xffffffffu, (m >> d) & 1u);
-            if (lane == 0) wt[warp * A2A_MAX_WORLD + d] = __popc(b);
+            const unsigned b = __ballot_sync(0xffffffffu, (mask >> d) & 1u);
+            if (lane == 0) m.wt[warp * A2A_MAX_WORLD + d] = __popc(b);
         }
         __syncthreads();
 #pragma unroll
         for (int d = 0; d < A2A_MAX_WORLD; ++d) {
-            const unsigned b = __ballot_sync(0xffffffffu, (m >> d) & 1u);
+            const unsigned b = __ballot_sync(0xffffffffu, (mask >> d) & 1u);
             int before = 0, total = 0;
             for (int w = 0; w < kThreads / 32; ++w) {
-                const int c = wt[w * A2A_MAX_WORLD + d];
+                const int c = m.wt[w * A2A_MAX_WORLD + d];
                 if (w < warp) before += c;
                 total += c;
             }
-            if ((m >> d) & 1u) {
+            if ((mask >> d) & 1u) {
                 const int n = base[d] + before + __popc(b & ((1u << lane) - 1u));
-                if (n % ns == sb) list[d * per + n / ns] = (unsigned short)t;
+                if (n % ns == sb) m.list[d * m.per + n / ns] = (unsigned short)t;
             }
             base[d] += total;
         }
@@ -145,7 +160,26 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
     }
     if (tid == 0) {
 #pragma unroll
-        for (int d = 0; d < A2A_MAX_WORLD; ++d) s_cnt[d] = base[d];
+        for (int d = 0; d < A2A_MAX_WORLD; ++d) cnt[d] = base[d];
+    }
+}
+
+// Sender block `sb` of `ns`, 16-bit payload: all threads build the block's token lists; then
+// thread 0 drives the copy engine (rows go HBM -> shared-memory ring -> peer without touching a
+// register) while, if `watch_kind` >= 0, warps 1.. watch the peers' flags of that kind (they
+// start only after the set-up barrier: a watcher may wait for a long time).
+__device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, int sb, int ns, int watch_kind,
+                                            int watch_phase) {
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const SenderSmem m = carve_sender(p, smem, ns);
+    uint8_t* ring = m.ring;
+    unsigned long long* bars = m.bars;
+    SendDesc* desc = m.desc;
+    unsigned short* list = m.list;
+    const int per = m.per;
+    __shared__ int s_cnt[A2A_MAX_WORLD];
+    build_send_lists(p, m, sb, ns, s_cnt);
+    if (tid == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(smem_addr(bars + s), 1);
         mbar_fence_init();
     }
@@ -156,7 +190,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
     }
 
     // ---- one thread drives the copy engine ----------------------------------------------
-    const uint32_t expected = (uint32_t)ns + 1u;  // every sender block + the destination's router
+    const uint32_t expected = (uint32_t)(ns + p.routers);  // every sender block + the destination's router blocks
     auto arrive = [&](int d) {
         arrive_dest(p, d, expected);
         stamp(p, kStampDestDone + (d - p.rank + p.ws) % p.ws);
@@ -246,11 +280,121 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
     if (pend_d >= 0 && !failed) arrive(pend_d);
 }
 
+// Sender block `sb` of `ns`, FP8 payload: a warp per wire row.  The warp reads the row with
+// 16-byte loads (eight in flight per lane), quantises it to e4m3 with one fp32 scale per 128
+// values into its own stage of the ring, and lane 0 hands the finished wire row to the copy
+// engine.  Dedicated watcher blocks poll the flags (every warp here is busy).
+constexpr int kWarpStageBytes = kStages * kStageBytes / (kThreads / 32);  // 12 KB per warp
+
+template <typename T>
+__device__ __forceinline__ void sender_role_fp8(const DevParams& p, uint8_t* smem, int sb, int ns) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const SenderSmem m = carve_sender(p, smem, ns);
+    __shared__ int s_cnt[A2A_MAX_WORLD];
+    __shared__ int s_done[A2A_MAX_WORLD];
+    build_send_lists(p, m, sb, ns, s_cnt);
+    if (tid < A2A_MAX_WORLD) s_done[tid] = 0;
+    __syncthreads();
+    const uint32_t expected = (uint32_t)(ns + p.routers);
+    constexpr int kWarps = kThreads / 32;
+    uint8_t* stage = m.ring + (size_t)warp * kWarpStageBytes;
+    const int nvec = p.H >> 3;
+    // lane 0: a warp whose stores to d are complete books it; the block's last warp draws the ticket
+    auto warp_arrive = [&](int d) {
+        fence_async_global();
+        __threadfence();
+        if (atomicAdd(&s_done[d], 1) == kWarps - 1) {
+            __threadfence();
+            arrive_dest(p, d, expected);
+            stamp_by(p, kStampDestDone + (d - p.rank + p.ws) % p.ws, true);
+        }
+    };
+    int pend_d = -1, pend_age = 0;
+    bool used = false;
+    for (int i = 1; i < p.ws; ++i) {
+        const int d = (p.rank + i) % p.ws;
+        const int mine = s_cnt[d] > sb ? (s_cnt[d] - sb + ns - 1) / ns : 0;
+        bool any = false;
+        for (int g = warp; g < mine; g += kWarps) {
+            const int n = sb + g * ns;
+            const int t = m.list[d * m.per + g];
+            if (used) {
+                if (lane == 0) bulk_wait_read<0>();  // the previous store has read this warp's stage
+                __syncwarp();
+            }
+            const uint4* src = reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec;
+            for (int v0 = 0; v0 < nvec; v0 += 256) {
+                uint4 q[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int v = v0 + u * 32 + lane;
+                    if (v < nvec) q[u] = ld_input(src + v);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int v = v0 + u * 32 + lane;  // nvec % 16 == 0: the 16 lanes of a scale block are all in or all out
+                    float f[8];
+                    float amax = 0.f;
+                    if (v < nvec) {
+                        unpack8<T>(q[u], f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+                    }
+#pragma unroll
+                    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    if (v < nvec) {
+                        const float sc = amax > 0.f ? amax / 448.f : 1.f;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) f[e] = f[e] / sc;
+                        reinterpret_cast<uint2*>(stage)[v] = pack8_e4m3(f);
+                        if ((v & 15) == 0) reinterpret_cast<float*>(stage + p.H)[v >> 4] = sc;
+                    }
+                }
+            }
+            fence_async_smem();  // the warp's ordinary stores to its stage, before the copy engine reads it
+            __syncwarp();
+            if (lane == 0) {
+                uint8_t* dst = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + n) * p.stage_row_bytes;
+                bulk_store(dst, smem_addr(stage), (uint32_t)p.stage_row_bytes);
+                bulk_commit();
+                if (pend_d >= 0 && ++pend_age >= 2) {
+                    bulk_wait_done(pend_age);
+                    warp_arrive(pend_d);
+                    pend_d = -1;
+                }
+            }
+            used = true;
+            any = true;
+        }
+        if (lane == 0) {
+            if (pend_d >= 0 && any) {  // an older destination is still pending: its stores precede this one's
+                bulk_wait_done(pend_age);
+                warp_arrive(pend_d);
+                pend_d = -1;
+            }
+            if (any) {
+                pend_d = d;
+                pend_age = 0;
+            } else {
+                warp_arrive(d);  // nothing of this warp goes there
+            }
+        }
+    }
+    if (lane == 0) {
+        bulk_wait_done(0);
+        if (pend_d >= 0) warp_arrive(pend_d);
+    }
+}
+
 // ---------------------------------------------------------------------------
-// Router block of destination rank d (all kThreads threads).  `first` marks the one
-// router that books the pairs nobody owns (expert index out of range).
+// Router block `part` of `nparts` of destination rank d (all kThreads threads).  Every part
+// builds the whole bitmap of d's experts (cheap, shared memory) but writes the records of its
+// own slice of the tokens only (32-token words w with w % nparts == part): the scattered stores
+// of one destination's records are spread over several SMs.  `first` marks the one router
+// that books the pairs nobody owns (expert index out of range).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, int d, bool first, uint32_t expected) {
+__device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, int d, int part, int nparts, bool first,
+                                            uint32_t expected) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int L = p.L, K = p.K, T = p.T;
     const int Wc = (T + 31) >> 5;
@@ -279,7 +423,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
                     }
                 } else if (e >= e0 && e < e0 + L) {
                     if (atomicOr(bits + (size_t)(t >> 5) * L + (e - e0), bit) & bit)  // a repeat inside the token
-                        record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
+                        if (part == 0) record_error(p.status, A2A_ERR_ROUTING, p.rank, -1, kPhaseRoute, p.epoch, e);
                 }
             }
         }
@@ -299,6 +443,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
     unsigned* rec_ent = reinterpret_cast<unsigned*>(there + p.off_rec_ent) + (size_t)p.rank * p.T_max * K;
     float* rec_w = reinterpret_cast<float*>(there + p.off_rec_w) + (size_t)p.rank * p.T_max * K;
     int* meta = reinterpret_cast<int*>(there + p.off_meta);
+    const bool vec = (K & 3) == 0;  // records of a token start on a 16-byte boundary: store them as vectors
     int base = 0;
     for (int r0 = 0; r0 < T; r0 += kThreads) {
         const int t = r0 + tid;
@@ -318,7 +463,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
             if (w < warp) before += wt[w];
             total += wt[w];
         }
-        if (has) {
+        if (has && ((t >> 5) % nparts) == part) {
             const int n = base + before + __popc(b & ((1u << lane) - 1u));  // wire row of token t at d
             const int* row = p.idx + (size_t)t * K;
             const float* wrow = p.w + (size_t)t * K;
@@ -328,6 +473,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
             for (int k0 = 0; k0 < K; k0 += 8) {
                 int e8[8];
                 float w8[8];
+                unsigned ent8[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     e8[u] = (k0 + u < K) ? __ldg(row + k0 + u) : -1;
@@ -336,40 +482,53 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const int k = k0 + u, e = e8[u];
-                    if (k >= K) break;
-                    unsigned ent = kNoEntry;
-                    if (e >= e0 && e < e0 + L) {
+                    ent8[u] = kNoEntry;
+                    if (k < K && e >= e0 && e < e0 + L) {
                         bool repeat = false;
                         for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
                         if (!repeat) {
                             const int l = e - e0, w = t >> 5;
                             const int j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (t & 31)) - 1u));
-                            ent = ((unsigned)l << 16) | (unsigned)j;
+                            ent8[u] = ((unsigned)l << 16) | (unsigned)j;
                             meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (t << 8) | k;
                             p.slot[(size_t)t * K + k] = j;
                         } else {
                             p.slot[(size_t)t * K + k] = -1;
                         }
                     }
-                    rec_ent[(size_t)n * K + k] = ent;
-                    rec_w[(size_t)n * K + k] = w8[u];
+                }
+                if (vec) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        if (k0 + 4 * h < K) {
+                            *reinterpret_cast<uint4*>(rec_ent + (size_t)n * K + k0 + 4 * h) =
+                                make_uint4(ent8[4 * h], ent8[4 * h + 1], ent8[4 * h + 2], ent8[4 * h + 3]);
+                            *reinterpret_cast<float4*>(rec_w + (size_t)n * K + k0 + 4 * h) =
+                                make_float4(w8[4 * h], w8[4 * h + 1], w8[4 * h + 2], w8[4 * h + 3]);
+                        }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (k0 + u < K) {
+                            rec_ent[(size_t)n * K + k0 + u] = ent8[u];
+                            rec_w[(size_t)n * K + k0 + u] = w8[u];
+                        }
                 }
             }
         }
         base += total;
         __syncthreads();
     }
-    int* counts = reinterpret_cast<int*>(there + p.off_counts) + (size_t)p.rank * kMaxChunks * L;
-    for (int l = tid; l < L; l += kThreads) {
-        counts[l] = cnt[l];
-        p.send_counts[e0 + l] = cnt[l];
+    if (part == 0) {
+        int* counts = reinterpret_cast<int*>(there + p.off_counts) + (size_t)p.rank * kMaxChunks * L;
+        for (int l = tid; l < L; l += kThreads) {
+            counts[l] = cnt[l];
+            p.send_counts[e0 + l] = cnt[l];
+        }
+        if (tid == 0) reinterpret_cast<int*>(there + p.off_hdr)[p.rank * 8] = base;
     }
-    if (tid == 0) reinterpret_cast<int*>(there + p.off_hdr)[p.rank * 8] = base;
     __syncthreads();
-    if (tid == 0) {
-        if (d == p.rank) st_release_gpu(seen_ptr(p, kFlagDispatch, p.rank), flag_value(p, 0));  // fence.gpu + store
-        else arrive_dest(p, d, expected);
-    }
+    if (tid == 0) arrive_dest(p, d, expected);
 }
 
 // One 128-vector (2 KB) chunk of a wire row as four 16-byte vectors of T per lane.
@@ -418,36 +577,92 @@ __device__ __forceinline__ void load_wire_chunk(const DevParams& p, bool own, co
 }
 
 // ---------------------------------------------------------------------------
-// Expert block `xb` of `nxb`: sources in arrival order; per source every warp of every
-// expert block takes (wire row, 2 KB chunk) items round-robin, continuing across sources
-// where the previous one left off, so no warp idles at a source boundary.
+// Expert block `xb` of `nxb`.  Sources are taken in arrival order (own rank first, then
+// rank-1, rank-2, ...).  Inside a block the warps have fixed jobs so that no source ever waits
+// for the bookkeeping of the one before it:
+//   warp 0 (lane 0)  poller: waits for the sources' dispatch flags in order, reads each source's
+//                    row count and raises a shared-memory word the workers spin on;
+//   warp 1           completer: joins the workers of source i at named barrier 1+i, then fences
+//                    (gpu scope; this is where the stores to the home rank are waited for) and draws
+//                    the block's ticket for that source -- the last ticket publishes the expert flag;
+//   warps 2..7       workers: every worker warp of every expert block takes (wire row, 2 KB chunk)
+//                    items round-robin, continuing across sources where the previous one left off;
+//                    having stored its share of source i a warp ARRIVES at barrier 1+i without waiting
+//                    and goes on to source i+1.
 // ---------------------------------------------------------------------------
+constexpr int kExpertWorkers = kThreads / 32 - 2;
+constexpr int kExpertBarThreads = (kExpertWorkers + 1) * 32;  // workers + completer
+
 template <typename T, int PAYLOAD, bool PUSH>
 __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb) {
-    __shared__ int s_ok;
-    const int tid = threadIdx.x, lane = tid & 31;
+    __shared__ volatile int s_seen[A2A_MAX_WORLD];  // 0 waiting, 1 rows of source position i are here, -1 gave up
+    __shared__ volatile int s_rows[A2A_MAX_WORLD];  // wire rows of source position i
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, nvec = p.H >> 3;
     const int nchunk = (nvec + 127) >> 7;
-    const int xw = xb * (kThreads / 32) + (tid >> 5);
-    const int nxw = nxb * (kThreads / 32);
     const uint32_t want = flag_value(p, 0);
-    const float scale = (float)(1 + p.rank);
     uint8_t* self = p.peer[p.rank];
+    if (tid < A2A_MAX_WORLD) s_seen[tid] = 0;
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int i = 0; i < p.ws; ++i) {
+                const int s = (p.rank - i + p.ws) % p.ws;
+                ok = ok && wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s);
+                int n_s = 0;
+                if (ok) {
+                    n_s = ld_stream(reinterpret_cast<const int*>(self + p.off_hdr) + s * 8);
+                    if (n_s < 0 || n_s > p.T_max) {
+                        record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, n_s);
+                        n_s = 0;
+                    }
+                }
+                s_rows[i] = n_s;
+                __threadfence_block();
+                s_seen[i] = ok ? 1 : -1;  // after a timeout every later source is given up as well
+                stamp_by(p, kStampSourceSeen + i, ok);
+            }
+        }
+        return;
+    }
+    if (warp == 1) {
+        for (int i = 0; i < p.ws; ++i) {
+            named_bar_sync(1 + i, kExpertBarThreads);  // every worker warp has stored its share of source i
+            if (lane == 0 && s_seen[i] == 1) {
+                const int s = (p.rank - i + p.ws) % p.ws;
+                __threadfence();
+                uint32_t* ticket = p.ptickets + kPipeTicketSource * A2A_MAX_WORLD + s;
+                if (atomicAdd(ticket, 1u) == (uint32_t)nxb - 1u) {
+                    *ticket = 0;
+                    if (s == p.rank) {
+                        st_release_gpu(seen_ptr(p, kFlagExpert, p.rank), want);
+                    } else {
+                        fence_acq_rel_sys();
+                        st_relaxed_sys(flag_ptr(p.peer[s], p.off_flags, kFlagExpert, p.rank), want);
+                    }
+                }
+                stamp_by(p, kStampSourceDone + i, true);
+            }
+            __syncwarp();
+        }
+        return;
+    }
+    const int xw = xb * kExpertWorkers + (warp - 2);
+    const int nxw = nxb * kExpertWorkers;
+    const float scale = (float)(1 + p.rank);
     uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
     long long cursor = 0;
     for (int i = 0; i < p.ws; ++i) {
-        const int s = (p.rank - i + p.ws) % p.ws;
-        if (tid == 0) s_ok = wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s) ? 1 : 0;
-        __syncthreads();
-        const int ok = s_ok;
-        __syncthreads();
-        if (!ok) return;  // timeout recorded; nothing further is published from here
-        stamp(p, kStampSourceSeen + i);
-        int n_s = ld_stream(reinterpret_cast<const int*>(self + p.off_hdr) + s * 8);
-        if (n_s < 0 || n_s > p.T_max) {
-            record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, n_s);
-            n_s = 0;
+        int seen;
+        while ((seen = s_seen[i]) == 0) __nanosleep(40);  // bounded by the poller's own bounded wait
+        if (seen < 0) {
+            // nothing further is processed or published; the completer is still owed this warp's arrivals
+            for (int j = i; j < p.ws; ++j) named_bar_arrive(1 + j, kExpertBarThreads);
+            return;
         }
+        const int s = (p.rank - i + p.ws) % p.ws;
+        const int n_s = s_rows[i];
         const int* rec_tok = reinterpret_cast<const int*>(self + p.off_rec_tok) + (size_t)s * p.T_max;
         const unsigned* rec_ent = reinterpret_cast<const unsigned*>(self + p.off_rec_ent) + (size_t)s * p.T_max * K;
         const float* rec_w = reinterpret_cast<const float*>(self + p.off_rec_w) + (size_t)s * p.T_max * K;
@@ -456,7 +671,7 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
         for (long long it = (xw - cursor % nxw + nxw) % nxw; it < items; it += nxw) {
             const int n = (int)(it / nchunk), v0 = (int)(it - (long long)n * nchunk) * 128;
             const int t = ld_stream(rec_tok + n);
-            const unsigned my_ent = lane < K ? ld_stream(reinterpret_cast<const int*>(rec_ent) + (size_t)n * K + lane) : kNoEntry;
+            const unsigned my_ent = lane < K ? (unsigned)ld_stream(reinterpret_cast<const int*>(rec_ent) + (size_t)n * K + lane) : kNoEntry;
             const float my_w = (PUSH && lane < K) ? ld_stream(rec_w + (size_t)n * K + lane) : 0.f;
             if (t < 0 || t >= p.T_max) {
                 record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseRecv, p.epoch, t);
@@ -507,22 +722,8 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
             }
         }
         cursor += items;
-        // the block's share of source s is stored: draw a ticket, the last one tells s
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence();
-            uint32_t* ticket = p.ptickets + kPipeTicketSource * A2A_MAX_WORLD + s;
-            if (atomicAdd(ticket, 1u) == (uint32_t)nxb - 1u) {
-                *ticket = 0;
-                if (s == p.rank) {
-                    st_release_gpu(seen_ptr(p, kFlagExpert, p.rank), want);
-                } else {
-                    fence_acq_rel_sys();
-                    st_relaxed_sys(flag_ptr(p.peer[s], p.off_flags, kFlagExpert, p.rank), want);
-                }
-            }
-        }
-        stamp(p, kStampSourceDone + i);
+        __syncwarp();
+        named_bar_arrive(1 + i, kExpertBarThreads);
     }
 }
 
@@ -564,24 +765,35 @@ __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, in
         for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
-        while (mask) {
-            const int d = __ffs(mask) - 1;
+        while (mask) {  // two ranks' partial rows in flight at a time, added in rank order
+            const int d0 = __ffs(mask) - 1;
             mask &= mask - 1;
-            const uint4* row = ret + ((size_t)d * p.T_max + t) * nvec;
-            uint4 q[4];
+            const int d1 = mask ? __ffs(mask) - 1 : -1;
+            mask &= mask - 1;
+            const uint4* row0 = ret + ((size_t)d0 * p.T_max + t) * nvec;
+            const uint4* row1 = ret + ((size_t)(d1 < 0 ? d0 : d1) * p.T_max + t) * nvec;
+            uint4 q0[4], q1[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int v = v0 + u * 32 + lane;
-                if (v < nvec) q[u] = ld_stream(row + v);
+                if (v < nvec) {
+                    q0[u] = ld_stream(row0 + v);
+                    if (d1 >= 0) q1[u] = ld_stream(row1 + v);
+                }
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int v = v0 + u * 32 + lane;
                 if (v < nvec) {
                     float f[8];
-                    unpack8<T>(q[u], f);
+                    unpack8<T>(q0[u], f);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
+                    if (d1 >= 0) {
+                        unpack8<T>(q1[u], f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
+                    }
                 }
             }
         }
@@ -609,25 +821,41 @@ __device__ __forceinline__ void wait_all_experts(const DevParams& p) {
 // ---------------------------------------------------------------------------
 extern __shared__ __align__(128) uint8_t a2a_pipe_smem[];
 
-// The whole path in one cooperative launch.  Blocks [0, senders) send (0 and 1 also watch),
-// the next `ws` route first, and everything from `senders` on is an expert block.
+// Block mapping.  16-bit payloads: blocks [0, senders) send, 0 and 1 also carry the watchers in
+// their spare warps.  FP8: every warp of a sender block quantises, so blocks 0 and 1 only watch
+// and blocks [2, 2 + senders) send.  The next `ws` blocks route first, and every block after
+// the senders is an expert block.
+template <int PAYLOAD>
+__device__ __forceinline__ int watcher_blocks(const DevParams& p) { return (PAYLOAD == A2A_PAYLOAD_FP8 && p.ws > 1) ? 2 : 0; }
+
+// The whole path in one cooperative launch.
 template <typename T, int PAYLOAD, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 2) pipe_forward_kernel(const __grid_constant__ DevParams p) {
     const int G = (int)gridDim.x, b = (int)blockIdx.x;
     const int ns = p.ws > 1 ? p.senders : 0;
+    const int nw = watcher_blocks<PAYLOAD>(p);
     stamp(p, kStampStart);
-    if (b < ns) {
-        stamp_value(p, kStampRole, b < 2 ? (kRoleSender | kRoleWatcher) : kRoleSender);
-        sender_role(p, a2a_pipe_smem, b, ns, b == 0 ? kFlagDispatch : (b == 1 ? kFlagExpert : -1),
-                    b == 0 ? kPhaseRecv : kPhaseCombine);
+    if (b < nw) {
+        stamp_value(p, kStampRole, kRoleWatcher);
+        watcher_role(p, b == 0 ? kFlagDispatch : kFlagExpert, b == 0 ? kPhaseRecv : kPhaseCombine, (int)(threadIdx.x >> 5));
+    } else if (b < nw + ns) {
+        if (PAYLOAD == A2A_PAYLOAD_FP8) {
+            stamp_value(p, kStampRole, kRoleSender);
+            sender_role_fp8<T>(p, a2a_pipe_smem, b - nw, ns);
+        } else {
+            stamp_value(p, kStampRole, b < 2 ? (kRoleSender | kRoleWatcher) : kRoleSender);
+            sender_role(p, a2a_pipe_smem, b, ns, b == 0 ? kFlagDispatch : (b == 1 ? kFlagExpert : -1),
+                        b == 0 ? kPhaseRecv : kPhaseCombine);
+        }
         stamp(p, kStampSent);
     } else {
-        const int xb = b - ns, nxb = G - ns;
-        if (xb < p.ws) {
-            router_role(p, a2a_pipe_smem, (p.rank + 1 + xb) % p.ws, xb == 0, (uint32_t)ns + 1u);
+        const int xb = b - nw - ns, nxb = G - nw - ns;
+        if (xb < p.ws * p.routers) {  // router part xb / ws of destination rank+1+(xb % ws): first needed, first served
+            const int d = (p.rank + 1 + xb % p.ws) % p.ws;
+            router_role(p, a2a_pipe_smem, d, xb / p.ws, p.routers, xb == 0, (uint32_t)(d == p.rank ? 0 : ns) + p.routers);
             stamp(p, kStampSent);
         }
-        stamp_value(p, kStampRole, xb < p.ws ? (kRoleExpert | kRoleRouter) : kRoleExpert);
+        stamp_value(p, kStampRole, xb < p.ws * p.routers ? (kRoleExpert | kRoleRouter) : kRoleExpert);
         expert_role<T, PAYLOAD, PUSH>(p, xb, nxb);
     }
     __syncthreads();
@@ -650,8 +878,13 @@ __global__ void __launch_bounds__(kThreads, 2) pipe_role_kernel(const __grid_con
     const int ns = p.ws > 1 ? p.senders : 0;
     stamp(p, kStampStart);
     if (ROLE == 0) {
-        if (b < ns) sender_role(p, a2a_pipe_smem, b, ns, -1, 0);
-        else router_role(p, a2a_pipe_smem, (p.rank + 1 + (b - ns)) % p.ws, b == ns, (uint32_t)ns + 1u);
+        if (b < ns) {
+            if (PAYLOAD == A2A_PAYLOAD_FP8) sender_role_fp8<T>(p, a2a_pipe_smem, b, ns);
+            else sender_role(p, a2a_pipe_smem, b, ns, -1, 0);
+        } else {
+            const int rb = b - ns, d = (p.rank + 1 + rb % p.ws) % p.ws;
+            router_role(p, a2a_pipe_smem, d, rb / p.ws, p.routers, rb == 0, (uint32_t)(d == p.rank ? 0 : ns) + p.routers);
+        }
         stamp(p, kStampSent);
     } else if (ROLE == 1) {
         if (b == 0) watcher_role(p, kFlagDispatch, kPhaseRecv, (int)(threadIdx.x >> 5));

@@ -53,7 +53,7 @@ enum {
     A2A_SCHEDULE_PHASED = 0,    /* routing, sending, expert pass and combine one after the other      */
     A2A_SCHEDULE_PIPELINED = 1  /* blocks with fixed roles (senders driving the copy engine, routers,
                                    experts, watchers) run the phases concurrently, per peer; needs the
-                                   DEDUP payload and a device with cooperative launch                */
+                                   DEDUP or FP8 payload and a device with cooperative launch         */
 };
 
 /* How expert outputs get back to the token's rank. */
@@ -85,7 +85,8 @@ typedef struct a2a_config {
     int32_t combine;         /* A2A_COMBINE_* (PUSH needs the pipelined schedule)            */
     int32_t chunks;          /* phased schedule: token chunks a call is pipelined in, 1..4;
                                 0 selects 1.  Every rank of a group must pass the same value */
-    int32_t senders;         /* pipelined schedule: blocks that only move rows; 0 selects 32 */
+    int32_t senders;         /* pipelined schedule: blocks that only move rows; 0 selects 32
+                                (64 with the FP8 payload, whose senders also quantise)       */
 } a2a_config;
 
 /* First error recorded by a kernel since the last a2a_status_clear(). */

@@ -14,7 +14,7 @@ from gpu_mode_kernels_b200 import _lib
 from gpu_mode_kernels_b200.all2all import A2AContext, A2AError, custom_kernel, release_contexts
 from gpu_mode_kernels_b200.local_world import LocalWorld
 from oracle import a2a_oracle as O
-from parity import tol
+from parity import check_y, fp8_roundtrip, tol
 
 pytestmark = pytest.mark.gpu
 
@@ -26,7 +26,7 @@ def bits(t):
     return t.contiguous().view(torch.int16)
 
 
-def check_pipelined_dispatch(world, disp, dtype):
+def check_pipelined_dispatch(world, disp, dtype, payload="dedup"):
     """After a pipelined forward the slabs hold the expert OUTPUT of every dispatched row:
     counts and (expert, source, token, k) must equal the reference's dispatch exactly, and every row
     must be bit-equal to dtype(float(reference row) * (1 + rank)) -- one rounding, as reference.py:262."""
@@ -39,23 +39,28 @@ def check_pipelined_dispatch(world, disp, dtype):
         gmeta = torch.cat([meta[e, : n[e]] for e in range(len(n))], 0).cpu()
         grows = torch.cat([rows[e, : n[e]] for e in range(len(n))], 0).cpu()
         assert torch.equal(gmeta, d.meta), f"rank {r}: meta/order differ"
-        want = (d.rows.float() * float(1 + r)).to(dtype)
+        rows_in = fp8_roundtrip(d.rows, dtype) if payload == "fp8" and d.rows.numel() else d.rows
+        want = (rows_in.float() * float(1 + r)).to(dtype)
         assert torch.equal(bits(grows), bits(want)), f"rank {r}: rows differ"
 
 
-def run_case(cfg, ws, rds_cpu, combine, tolerance=None):
+def run_case(cfg, ws, rds_cpu, combine, tolerance=None, payload="dedup"):
     disp, ys = O.simulate(cfg, ws, rds_cpu)
-    world = LocalWorld(cfg, ws, payload="dedup", schedule="pipelined", combine=combine)
+    world = LocalWorld(cfg, ws, payload=payload, schedule="pipelined", combine=combine)
     try:
         rds = [rd.to(DEV) for rd in rds_cpu]
         out = world.forward_pipelined(rds)
         torch.cuda.synchronize()
         world.check()
-        check_pipelined_dispatch(world, disp, cfg.in_dtype)
-        t = tolerance or tol(cfg.in_dtype)
+        check_pipelined_dispatch(world, disp, cfg.in_dtype, payload)
         for r in range(ws):
             assert out[r].shape == (rds_cpu[r].num_tokens, cfg.hidden_dim) and out[r].dtype == cfg.out_dtype
-            torch.testing.assert_close(out[r].cpu().float(), ys[r].float(), **t)
+        if payload == "fp8":
+            check_y(cfg, ws, rds_cpu, out, ys, payload)  # the FP8 rules of parity.py
+        else:
+            t = tolerance or tol(cfg.in_dtype)
+            for r in range(ws):
+                torch.testing.assert_close(out[r].cpu().float(), ys[r].float(), **t)
         return world, out
     except Exception:
         world.close()
@@ -113,6 +118,27 @@ def test_edge_shapes(E, K, H, T, ws, dtype, combine):
              for r in range(ws)]
     world, _ = run_case(datas[0][0], ws, [d[1] for d in datas], combine)
     world.close()
+
+
+@pytest.mark.parametrize("combine", COMBINES)
+@pytest.mark.parametrize("name,ws", [("c5", 8), ("c5", 2), ("c5", 1), ("c3", 8)])
+def test_fp8_payload(name, ws, combine):
+    """Config 5: the senders quantise each wire row to e4m3 + one fp32 scale per 128 values on the fly;
+    the expert rank dequantises.  Dispatch bit-exact against the checker's quantise -> dequantise of
+    the reference rows; combine under the FP8 rules (parity.py)."""
+    datas = [pkg.workload_input(name, r, ws) for r in range(ws)]
+    world, _ = run_case(datas[0][0], ws, [d[1] for d in datas], combine, payload="fp8")
+    world.close()
+
+
+@pytest.mark.parametrize("combine", COMBINES)
+def test_fp8_edge_shapes(combine):
+    for E, K, H, T, ws, dtype in [(8, 2, 128, 5, 2, torch.bfloat16), (16, 4, 2944, 70, 4, torch.float16),
+                                  (32, 4, 256, 700, 4, torch.bfloat16), (6, 3, 640, 33, 1, torch.float16)]:
+        datas = [pkg.generate_input(E, K, H, T, seed=6, rank=r, world_size=ws, dtype=dtype, ragged=True)
+                 for r in range(ws)]
+        world, _ = run_case(datas[0][0], ws, [d[1] for d in datas], combine, payload="fp8")
+        world.close()
 
 
 @pytest.mark.parametrize("spec", pkg.REFERENCE_TESTS + pkg.REFERENCE_BENCHMARKS,
@@ -291,7 +317,7 @@ def test_forward_refuses_tensors_it_would_misread():
         ctx.close()
 
 
-def test_pipelined_needs_the_dedup_payload_and_push_needs_pipelined():
+def test_pipelined_needs_a_wire_row_payload_and_push_needs_pipelined():
     cfg = pkg.MoEConfig(8, 2, 64, 4)
     for kw in (dict(payload="direct", schedule="pipelined"), dict(payload="dedup", schedule="phased", combine="push")):
         with pytest.raises(A2AError) as ei:

@@ -31,6 +31,7 @@ CASES = [
     (256, 8, 7168, 256, 3, 20, "dedup", "pipelined", "push"),
     (256, 8, 7168, 256, 3, 20, "dedup", "pipelined", "pull"),
     (64, 6, 2048, 1024, 7, 12, "dedup", "pipelined", "push"),
+    (256, 8, 7168, 256, 4, 20, "fp8", "pipelined", "push"),
 ]
 
 
