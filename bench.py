@@ -351,8 +351,8 @@ def main():
     ph_steps = min(args.steps, 200)
     if pipelined:
         names = ["send_route", "expert", "combine"]
-        calls = [lambda: ctx.pipe_step(0, rd.x, rd.indices, rd.weights), lambda: ctx.pipe_step(1),
-                 lambda: ctx.pipe_step(2, y=y)]
+        calls = [lambda: ctx.pipe_step(0, rd.x, rd.indices, rd.weights, y), lambda: ctx.pipe_step(1),
+                 lambda: ctx.pipe_step(2)]
     else:
         names = ["route", "dispatch_send", "recv_expert", "combine"]
         calls = [lambda: ctx.route(rd.indices), lambda: ctx.dispatch_send(rd.x), ctx.dispatch_recv_expert,

@@ -176,18 +176,20 @@ class A2AContext:
         return y
 
     def pipe_step(self, role: int, x=None, indices=None, weights=None, y=None) -> Optional[torch.Tensor]:
-        """One role of the pipelined kernel as its own launch: 0 senders + routers (x, indices,
-        weights), 1 experts, 2 combine (returns y).  For stepping several ranks on one GPU."""
-        n = self._num_tokens
+        """One role of the pipelined kernel as its own launch: 0 senders + routers (takes x, indices,
+        weights and optionally the output tensor), 1 experts, 2 combine (returns the output).  For
+        stepping several ranks on one GPU and for timing the roles apart."""
         if role == 0:
-            n = self._check_inputs(x, indices, weights, None, on_device=True)
-            self._num_tokens = n
-            self._keep = [x, indices, weights]
-        if role == 2 and y is None:
-            y = torch.empty(n, self.cfg.hidden_dim, dtype=self.cfg.out_dtype, device=self.device)
-        _lib.check(self.lib.a2a_pipe_step(self._h, role, _ptr(x), _ptr(indices), _ptr(weights), _ptr(y), n,
-                                          self._stream()))
-        return y
+            n = self._check_inputs(x, indices, weights, y, on_device=True)
+            if y is None:
+                y = torch.empty(n, self.cfg.hidden_dim, dtype=self.cfg.out_dtype, device=self.device)
+            self._num_tokens, self._y = n, y
+            self._keep = [x, indices, weights, y]
+            _lib.check(self.lib.a2a_pipe_step(self._h, 0, _ptr(x), _ptr(indices), _ptr(weights), _ptr(y), n,
+                                              self._stream()))
+            return None
+        _lib.check(self.lib.a2a_pipe_step(self._h, role, None, None, None, None, self._num_tokens, self._stream()))
+        return self._y if role == 2 else None
 
     def forward_host(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
                      y: Optional[torch.Tensor] = None) -> torch.Tensor:

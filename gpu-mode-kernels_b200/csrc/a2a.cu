@@ -701,20 +701,17 @@ int a2a_pipe_step(a2a_ctx* c, int role, const void* x, const int32_t* idx, const
     if (role == 0) {
         int r = begin_call(c, idx, T);
         if (r != A2A_OK) return r;
-        if (T > 0 && (x == nullptr || w == nullptr)) return A2A_ERR_CONFIG;
-        if (!rows_aligned(x) || reinterpret_cast<uintptr_t>(w) % 4 != 0) return A2A_ERR_CONFIG;
+        if (T > 0 && (x == nullptr || w == nullptr || y == nullptr)) return A2A_ERR_CONFIG;
+        if (!rows_aligned(x) || !rows_aligned(y) || reinterpret_cast<uintptr_t>(w) % 4 != 0) return A2A_ERR_CONFIG;
         c->p.x = x;
         c->p.w = w;
+        c->p.y = y;  // with one rank and the PUSH combine the expert blocks already write the output
         r = launch(c, pipe_fn(c, 0), c->p.senders + ws * c->p.routers, c->pipe_smem, st);
         if (r == A2A_OK) c->sent = true;
         return r;
     }
     if (!c->sent) return A2A_ERR_STATE;
-    if (role == 1) return launch(c, pipe_fn(c, 1), 1 + c->num_sms * 2, c->pipe_smem, st);
-    if (c->cur_tokens > 0 && y == nullptr) return A2A_ERR_CONFIG;
-    if (!rows_aligned(y)) return A2A_ERR_CONFIG;
-    c->p.y = y;
-    return launch(c, pipe_fn(c, 2), 1 + c->num_sms * 2, c->pipe_smem, st);
+    return launch(c, pipe_fn(c, role), 1 + c->num_sms * 2, c->pipe_smem, st);
 }
 
 int a2a_barrier(a2a_ctx* c, void* stream) {

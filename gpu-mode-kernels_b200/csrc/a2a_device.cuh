@@ -61,6 +61,10 @@ enum Stamp : int {
     kStampGlobalNs = 0, kStampStart, kStampRouted, kStampSent, kStampDispatchSeen, kStampExpertDone,
     kStampExpertSeen, kStampCombineDone, kStampRole = kStampRouted /* pipelined: what the block was */,
     kStampSourceSeen = 8, kStampSourceDone = 16, kStampDestDone = 24,
+    // finer steps inside a role, in slots that role does not use otherwise: a router block stamps
+    // kStampStep + {0 bitmap cleared, 1 bitmap built, 2 scanned, 3 records written}; a sender block
+    // kStampSetup + {0 token lists built, 1 first load issued, 2 first store issued}
+    kStampStep = 24, kStampSetup = 8,
     kNumStamps = 32
 };
 enum Role : int { kRoleSender = 1, kRoleExpert = 2, kRoleRouter = 4, kRoleWatcher = 8 };
@@ -287,9 +291,15 @@ __device__ __forceinline__ uint32_t* seen_ptr(const DevParams& p, int kind, int 
 // Watcher duty: wait for peer `index`'s flag of `kind` at system scope, then hand it to
 // the rest of this GPU through the local word.  On a timeout nothing is handed on and
 // the local waiters run into the recorded timeout.
+__device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ bool watch_and_republish(const DevParams& p, int kind, int index, int phase, uint32_t value) {
     const bool ok = wait_flag_sys(flag_ptr(p.peer[p.rank], p.off_flags, kind, index), value, p, phase, index);
-    if (ok) st_release_gpu(seen_ptr(p, kind, index), value);
+    // the system-scope acquire-release fence taken on success also is the release half of this store
+    // (a fence followed by a relaxed store releases at the fence's scope, which includes the gpu's)
+    if (ok) st_relaxed_gpu(seen_ptr(p, kind, index), value);
     return ok;
 }
 

@@ -184,6 +184,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
         mbar_fence_init();
     }
     __syncthreads();
+    stamp(p, kStampSetup + 0);
     if (tid != 0) {
         if (watch_kind >= 0 && warp > 0) watcher_role(p, watch_kind, watch_phase, warp - 1);
         return;
@@ -236,6 +237,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
             desc[st].dest_done = (last_piece && g_i == mine - 1) ? d : -1;
             mbar_expect_tx(smem_addr(bars + st), bytes);
             bulk_load(smem_addr(ring + (size_t)st * kStageBytes), src, bytes, smem_addr(bars + st));
+            if (q == 0) stamp(p, kStampSetup + 1);
             if (last_piece) {
                 g_piece = 0;
                 ++g_i;
@@ -261,6 +263,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
             if (failed) break;
             bulk_store(reinterpret_cast<void*>(desc[st].dst), smem_addr(ring + (size_t)st * kStageBytes), desc[st].bytes);
             bulk_commit();
+            if (it == 0) stamp(p, kStampSetup + 2);
             if (pend_d >= 0 && ++pend_age >= 2) {  // two more groups were committed since: the old one is through by now
                 bulk_wait_done(pend_age);
                 arrive(pend_d);
@@ -405,6 +408,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
     const int e0 = d * L;
     for (int i = tid; i < Wc * L; i += kThreads) bits[i] = 0u;
     __syncthreads();
+    stamp(p, kStampStep + 0);
     for (int t = tid; t < T; t += kThreads) {
         const int* row = p.idx + (size_t)t * K;
         const unsigned bit = 1u << (t & 31);
@@ -429,6 +433,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
         }
     }
     __syncthreads();
+    stamp(p, kStampStep + 1);
     for (int l = tid; l < L; l += kThreads) {
         int run = 0;
         for (int w = 0; w < Wc; ++w) {
@@ -438,6 +443,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
         cnt[l] = run;
     }
     __syncthreads();
+    stamp(p, kStampStep + 2);
     uint8_t* there = p.peer[d];
     int* rec_tok = reinterpret_cast<int*>(there + p.off_rec_tok) + (size_t)p.rank * p.T_max;
     unsigned* rec_ent = reinterpret_cast<unsigned*>(there + p.off_rec_ent) + (size_t)p.rank * p.T_max * K;
@@ -528,6 +534,7 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
         if (tid == 0) reinterpret_cast<int*>(there + p.off_hdr)[p.rank * 8] = base;
     }
     __syncthreads();
+    stamp(p, kStampStep + 3);
     if (tid == 0) arrive_dest(p, d, expected);
 }
 
@@ -713,7 +720,9 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
                 }
             }
             if (PUSH) {
-                uint4* home = reinterpret_cast<uint4*>(p.peer[s] + p.off_ret) + ((size_t)p.rank * p.T_max + t) * nvec;
+                // one rank: the partial row IS the token's output -- no return buffer, no combine pass
+                uint4* home = p.ws == 1 ? reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec
+                                        : reinterpret_cast<uint4*>(p.peer[s] + p.off_ret) + ((size_t)p.rank * p.T_max + t) * nvec;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int v = v0 + u * 32 + lane;
@@ -738,6 +747,30 @@ __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, in
     const int K = p.K, nvec = p.H >> 3;
     const int nchunk = (nvec + 127) >> 7;
     const uint32_t want = flag_value(p, 0);
+    if (p.ws == 1) {
+        // The expert blocks have written y themselves.  What is left are tokens none of whose pairs is
+        // valid (they have no wire row): their output is zero.  No flag is needed for that.
+        const long long items = (long long)p.T * nchunk;
+        const int cw = cb * (kThreads / 32) + (tid >> 5), ncw = ncb * (kThreads / 32);
+        for (long long it = cw; it < items; it += ncw) {
+            const int t = (int)(it / nchunk), v0 = (int)(it - (long long)t * nchunk) * 128;
+            bool any = false;
+            if (lane < K) {
+                const int e = __ldg(p.idx + (size_t)t * K + lane);
+                any = (e >= 0 && e < p.E);
+            }
+            if (__any_sync(0xffffffffu, any)) continue;
+            uint4* y = reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int v = v0 + u * 32 + lane;
+                if (v < nvec) st_stream(y + v, make_uint4(0u, 0u, 0u, 0u));
+            }
+        }
+        stamp(p, kStampExpertSeen);
+        stamp(p, kStampCombineDone);
+        return;
+    }
     if (tid == 0) {
         int ok = 1;
         for (int i = 0; i < p.ws && ok; ++i) {

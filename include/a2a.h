@@ -209,9 +209,9 @@ int a2a_forward_host(a2a_ctx* ctx, const void* x_host, const int32_t* topk_idx_h
                      const float* topk_weights_host, void* y_host, int num_tokens, void* stream);
 
 /* The roles of the pipelined one-launch kernel as three separate launches (same device code):
- * role 0 = senders + routers (takes x, topk_idx, topk_weights and num_tokens; starts the call),
- * role 1 = dispatch watchers + expert blocks, role 2 = expert-flag watchers + combine (takes y).
- * Arguments a role does not use may be NULL / 0.  For stepping several ranks on one GPU -- a
+ * role 0 = senders + routers (takes x, topk_idx, topk_weights, y and num_tokens; starts the call),
+ * role 1 = dispatch watchers + expert blocks, role 2 = expert-flag watchers + combine; roles 1
+ * and 2 take no tensors (NULL / 0): they use what role 0 was given.  For stepping several ranks on one GPU -- a
  * kernel that waits for a peer never shares a GPU with the kernel it waits for -- and for
  * timing the roles apart.  Needs a context created with A2A_SCHEDULE_PIPELINED.  The reference
  * splits its fused call the same way into dispatch and combine ops (submission_v9.py:675-731). */

@@ -95,7 +95,7 @@ def test_stamps_of_a_real_launch_are_ordered_and_tracing_off_writes_nothing(sche
             experts = st[(st[:, 2] & tracing.ROLE_EXPERT) != 0]
             assert experts.shape[0] == st.shape[0]  # world size 1: no sender blocks
             assert bool((experts[:, 8] >= experts[:, 1]).all()) and bool((experts[:, 16] >= experts[:, 8]).all())
-            assert int(((st[:, 2] & tracing.ROLE_ROUTER) != 0).sum()) == 1
+            assert 1 <= int(((st[:, 2] & tracing.ROLE_ROUTER) != 0).sum()) <= 8  # router blocks of the one destination
         ev = tracing.rank_events(st, 0, sm_mhz=1965.0, world_size=1)
         assert ev["blocks"] == st.shape[0] and len(ev["events"]) >= 3 * st.shape[0]
         assert all(0 <= e["ts"] < 1e4 and 0 <= e["dur"] < 1e4 for e in ev["events"])
