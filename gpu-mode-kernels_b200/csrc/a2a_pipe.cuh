@@ -40,7 +40,7 @@ enum PipeTicket : int { kPipeTicketDest = 0, kPipeTicketSource = 1 };
 
 // ---- shared memory of a block, carved per role --------------------------------------------
 // sender: ring [kStages][kStageBytes] | mbarriers [kStages] u64 | descriptors | list [ws][per] u16 | warp totals
-// router: bits [Wc][L] | wpre [Wc][L] | cnt [L] | warp totals
+// router: bits [Wc][L] | wpre [Wc][L] | cnt [L] | warp totals | wire row of each token of a round
 __host__ __device__ inline int pipe_list_per(int T_max, int senders) { return (T_max + senders - 1) / (senders > 0 ? senders : 1); }
 
 __host__ __device__ inline size_t pipe_sender_smem(int T_max, int ws, int senders) {
@@ -53,7 +53,7 @@ __host__ __device__ inline size_t pipe_sender_smem(int T_max, int ws, int sender
 
 __host__ __device__ inline size_t pipe_router_smem(int T_max, int L) {
     const size_t W = (size_t)(T_max + 31) / 32;
-    return (2 * W * L + L + 16) * 4;
+    return (2 * W * L + L + 16 + 256) * 4;  // bitmap, prefix, counts, warp totals, wire row of a round's tokens
 }
 
 struct SendDesc {
@@ -449,7 +449,11 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
     unsigned* rec_ent = reinterpret_cast<unsigned*>(there + p.off_rec_ent) + (size_t)p.rank * p.T_max * K;
     float* rec_w = reinterpret_cast<float*>(there + p.off_rec_w) + (size_t)p.rank * p.T_max * K;
     int* meta = reinterpret_cast<int*>(there + p.off_meta);
-    const bool vec = (K & 3) == 0;  // records of a token start on a 16-byte boundary: store them as vectors
+    // Records, 256 tokens at a time.  First a thread per token: which tokens have a row at d, and by
+    // ballot / popc compaction which wire row n each of them is.  Then a thread per (token, k) pair:
+    // consecutive threads handle consecutive pairs, so the index / weight loads and the record stores
+    // are coalesced and all warps of the block are busy even when its slice of the tokens is small.
+    int* n_of = wt + 16; // [kThreads] wire row of the round's token, or -1 (not ours / no row at d)
     int base = 0;
     for (int r0 = 0; r0 < T; r0 += kThreads) {
         const int t = r0 + tid;
@@ -469,60 +473,39 @@ __device__ __forceinline__ void router_role(const DevParams& p, uint8_t* smem, i
             if (w < warp) before += wt[w];
             total += wt[w];
         }
+        int n = -1;
         if (has && ((t >> 5) % nparts) == part) {
-            const int n = base + before + __popc(b & ((1u << lane) - 1u));  // wire row of token t at d
-            const int* row = p.idx + (size_t)t * K;
-            const float* wrow = p.w + (size_t)t * K;
+            n = base + before + __popc(b & ((1u << lane) - 1u));  // wire row of token t at d
             rec_tok[n] = t;
-            // eight pairs at a time: their indices and weights are loaded together (one memory latency,
-            // not one per pair) before anything is stored
-            for (int k0 = 0; k0 < K; k0 += 8) {
-                int e8[8];
-                float w8[8];
-                unsigned ent8[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    e8[u] = (k0 + u < K) ? __ldg(row + k0 + u) : -1;
-                    w8[u] = (k0 + u < K) ? __ldg(wrow + k0 + u) : 0.f;
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int k = k0 + u, e = e8[u];
-                    ent8[u] = kNoEntry;
-                    if (k < K && e >= e0 && e < e0 + L) {
-                        bool repeat = false;
-                        for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
-                        if (!repeat) {
-                            const int l = e - e0, w = t >> 5;
-                            const int j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (t & 31)) - 1u));
-                            ent8[u] = ((unsigned)l << 16) | (unsigned)j;
-                            meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (t << 8) | k;
-                            p.slot[(size_t)t * K + k] = j;
-                        } else {
-                            p.slot[(size_t)t * K + k] = -1;
-                        }
-                    }
-                }
-                if (vec) {
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        if (k0 + 4 * h < K) {
-                            *reinterpret_cast<uint4*>(rec_ent + (size_t)n * K + k0 + 4 * h) =
-                                make_uint4(ent8[4 * h], ent8[4 * h + 1], ent8[4 * h + 2], ent8[4 * h + 3]);
-                            *reinterpret_cast<float4*>(rec_w + (size_t)n * K + k0 + 4 * h) =
-                                make_float4(w8[4 * h], w8[4 * h + 1], w8[4 * h + 2], w8[4 * h + 3]);
-                        }
-                } else {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (k0 + u < K) {
-                            rec_ent[(size_t)n * K + k0 + u] = ent8[u];
-                            rec_w[(size_t)n * K + k0 + u] = w8[u];
-                        }
-                }
-            }
         }
+        n_of[tid] = n;
         base += total;
+        __syncthreads();
+        const int round_tokens = min(kThreads, T - r0);
+        for (int q = tid; q < round_tokens * K; q += kThreads) {
+            const int tl = q / K, k = q - tl * K;
+            const int nn = n_of[tl];
+            if (nn < 0) continue;
+            const int tt = r0 + tl;
+            const int* row = p.idx + (size_t)tt * K;
+            const int e = __ldg(row + k);
+            const float wk = __ldg(p.w + (size_t)tt * K + k);
+            unsigned ent = kNoEntry;
+            if (e >= e0 && e < e0 + L) {
+                bool repeat = false;
+                for (int kk = 0; kk < k; ++kk) repeat |= (__ldg(row + kk) == e);
+                int j = -1;
+                if (!repeat) {
+                    const int l = e - e0, w = tt >> 5;
+                    j = wpre[(size_t)w * L + l] + __popc(bits[(size_t)w * L + l] & ((1u << (tt & 31)) - 1u));
+                    ent = ((unsigned)l << 16) | (unsigned)j;
+                    meta[((size_t)l * p.ws + p.rank) * p.T_max + j] = (tt << 8) | k;
+                }
+                p.slot[(size_t)tt * K + k] = j;
+            }
+            rec_ent[(size_t)nn * K + k] = ent;
+            rec_w[(size_t)nn * K + k] = wk;
+        }
         __syncthreads();
     }
     if (part == 0) {
