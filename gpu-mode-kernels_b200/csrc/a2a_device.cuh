@@ -410,16 +410,19 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N>
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 
-// At most n (0..3; larger waits for 3) of this thread's most recent bulk groups may still be pending
+// At most n (0..5; larger waits for 5) of this thread's most recent bulk groups may still be pending
 // at all: the older ones have written their destination.
 __device__ __forceinline__ void bulk_wait_done(int n) {
     switch (n) {
         case 0: asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); break;
         case 1: asm volatile("cp.async.bulk.wait_group 1;" ::: "memory"); break;
         case 2: asm volatile("cp.async.bulk.wait_group 2;" ::: "memory"); break;
-        default: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.bulk.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); break;
+        default: asm volatile("cp.async.bulk.wait_group 5;" ::: "memory"); break;
     }
 }
+constexpr int kArrivalLag = 4;  // stores a sender issues after a destination's last one before it waits for that one
 
 // Orders the copy engine's accesses to global memory with this thread's ordinary ones.
 __device__ __forceinline__ void fence_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }

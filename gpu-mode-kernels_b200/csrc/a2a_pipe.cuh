@@ -264,7 +264,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
             bulk_store(reinterpret_cast<void*>(desc[st].dst), smem_addr(ring + (size_t)st * kStageBytes), desc[st].bytes);
             bulk_commit();
             if (it == 0) stamp(p, kStampSetup + 2);
-            if (pend_d >= 0 && ++pend_age >= 2) {  // two more groups were committed since: the old one is through by now
+            if (pend_d >= 0 && ++pend_age >= kArrivalLag) {  // that many groups later the old one has been acknowledged, or nearly
                 bulk_wait_done(pend_age);
                 arrive(pend_d);
                 pend_d = -1;
@@ -360,7 +360,7 @@ __device__ __forceinline__ void sender_role_fp8(const DevParams& p, uint8_t* sme
                 uint8_t* dst = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + n) * p.stage_row_bytes;
                 bulk_store(dst, smem_addr(stage), (uint32_t)p.stage_row_bytes);
                 bulk_commit();
-                if (pend_d >= 0 && ++pend_age >= 2) {
+                if (pend_d >= 0 && ++pend_age >= kArrivalLag) {
                     bulk_wait_done(pend_age);
                     warp_arrive(pend_d);
                     pend_d = -1;
@@ -754,13 +754,10 @@ __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, in
         stamp(p, kStampCombineDone);
         return;
     }
-    if (tid == 0) {
-        int ok = 1;
-        for (int i = 0; i < p.ws && ok; ++i) {
-            const int d = (p.rank + i) % p.ws;
-            ok = wait_flag_gpu(seen_ptr(p, kFlagExpert, d), want, p, kPhaseCombine, d) ? 1 : 0;
-        }
-        s_ok = ok;
+    if (tid < 32) {  // lane d waits for rank d's flag: all of them at once, not one after the other
+        const bool ok = tid >= p.ws || wait_flag_gpu(seen_ptr(p, kFlagExpert, tid), want, p, kPhaseCombine, tid);
+        const bool all = __all_sync(0xffffffffu, ok);
+        if (tid == 0) s_ok = all ? 1 : 0;
     }
     __syncthreads();
     if (!s_ok) return;  // timeout recorded; y is left untouched
