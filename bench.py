@@ -261,6 +261,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if ws == 1 and args.gpus > 1:
         sys.exit("bench.py --gpus N>1 must be launched with python -m torch.distributed.run --nproc-per-node N")
+    if args.workload == "histogram":
+        histogram_main(args, rank, ws)
+        return
     if args.impl == "reference":
         reference_main(args, rank, ws)
         return
@@ -526,6 +529,95 @@ def main():
     if ws > 1:
         dist.destroy_process_group()
     if verified is not None and rank == 0 and not verified["ok"]:
+        sys.exit(3)
+
+
+def histogram_main(args, rank: int, ws: int):
+    """`--workload histogram`: the reference repository's second task (pmpp_v2/histogram_py) on its
+    largest benchmark case, 10 485 760 bytes at 10 % contention (task.yml:39).  Does not shard: with
+    N > 1 every rank runs its own replica ("replicas only"); rank 0 reports one replica's time."""
+    if rank != 0:
+        return
+    from oracle import histogram_oracle as HO
+
+    size, seed, contention = HO.REFERENCE_BENCHMARKS[-1]
+    data_cpu, _ = HO.generate_input(size, contention, seed)
+    if args.impl == "reference":
+        torch.set_num_threads(os.cpu_count() or 1)
+        times = []
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            torch.bincount(data_cpu, minlength=256)  # the reference's own call (reference.py:17), on the host cores
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        us = 1e6 * sum(times) / len(times)
+        print(json.dumps({"impl": "reference", "metric": "histogram us", "value": us, "unit": "us", "n_gpus": ws,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+                          "config": {"workload": f"histogram: {size} bytes, contention {contention} %, seed {seed}"},
+                          "cpu_baseline": {"value": us, "unit": "us", "cores": torch.get_num_threads(), "kind": "reference",
+                                           "sample": "torch.bincount(data, minlength=256) on the full input"},
+                          "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}), flush=True)
+        return
+    from gpu_mode_kernels_b200.histogram import histogram256
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    data = data_cpu.to(dev)
+    out = torch.empty(256, dtype=torch.int64, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.int8, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def loop(fn, steps, warmup):
+        for i in range(warmup):
+            flush.fill_(i & 1)
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i in range(steps):
+            flush.fill_(i & 1)
+            ev[i][0].record(stream)
+            fn()
+            ev[i][1].record(stream)
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in ev]
+
+    with ClockSampler(physical_gpu_index(0)) as clocks:
+        ms_list = loop(lambda: histogram256(data, out), args.steps, args.warmup)
+    ok = bool(torch.equal(out.cpu(), HO.ref_histogram(data_cpu)))
+    ms = sum(ms_list) / len(ms_list)
+    host = data_cpu.pin_memory()
+    host_out = torch.empty(256, dtype=torch.int64, pin_memory=True)
+
+    def e2e():
+        data.copy_(host, non_blocking=True)
+        histogram256(data, out)
+        host_out.copy_(out, non_blocking=True)
+
+    e2e_ms = loop(e2e, min(args.steps, 100), 5)
+    hbm_peak, peak_kind = measured_peaks()
+    alg = size + 256 * 8
+    t0 = time.perf_counter()
+    for _ in range(5):
+        torch.bincount(data_cpu, minlength=256)
+    cpu_us = 1e6 * (time.perf_counter() - t0) / 5
+    print(json.dumps({
+        "metric": "histogram us", "value": ms * 1e3, "unit": "us", "n_gpus": ws, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": f"histogram: {size} bytes, contention {contention} %, seed {seed}; replicas only",
+                   "l2": "flushed between timed steps (256 MiB write, untimed)"},
+        "roofline": {"bound": "hbm", "kernel": "histogram256_kernel (+ 2 KB memset)", "achieved": alg / (ms * 1e-3) / 1e9,
+                     "peak": hbm_peak, "unit": "GB/s", "frac": alg / (ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "algorithmic_bytes": alg},
+        "cpu_baseline": {"value": cpu_us, "unit": "us", "cores": torch.get_num_threads(), "kind": "reference",
+                         "sample": "torch.bincount(data, minlength=256) on the full input, mean of 5"},
+        "e2e": {"value": 1e3 * sum(e2e_ms) / len(e2e_ms), "unit": "us", "h2d_bytes_per_step": size, "d2h_bytes_per_step": 2048},
+        "gpu_launches": args.steps, "clocks": clocks.summary(), "verified": {"ok": ok, "how": "counts equal torch.bincount on the CPU"},
+        "p50_us": 1e3 * statistics.median(ms_list), "p95_us": 1e3 * percentile(ms_list, 0.95),
+    }), flush=True)
+    if not ok:
         sys.exit(3)
 
 

@@ -68,6 +68,7 @@ SIGNATURES = {
     "a2a_route_buffers": (_I, [_VP, C.POINTER(_VP), C.POINTER(_VP)]),
     "a2a_copy_route": (_I, [_VP, _VP, _VP, _VP]),
     "a2a_route_noalloc": (_I, [_VP, _I, _I, _I, _VP, _VP, _VP]),
+    "a2a_histogram256": (_I, [_VP, C.c_size_t, _VP, _VP]),
     "a2a_status": (_I, [_VP, C.POINTER(Status)]),
     "a2a_status_clear": (_I, [_VP]),
     "a2a_status_peek": (_I, [_VP]),

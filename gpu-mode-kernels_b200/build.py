@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "liba2a.so")
-SOURCES = [os.path.join(CSRC, "a2a.cu"), os.path.join(CSRC, "a2a_noalloc.cu")]
+SOURCES = [os.path.join(CSRC, "a2a.cu"), os.path.join(CSRC, "a2a_noalloc.cu"), os.path.join(CSRC, "histogram.cu")]
 HEADERS = [os.path.join(CSRC, "a2a_kernels.cuh"), os.path.join(CSRC, "a2a_pipe.cuh"), os.path.join(CSRC, "a2a_device.cuh"),
            os.path.join(ROOT, "include", "a2a.h")]
 

@@ -269,6 +269,13 @@ int a2a_copy_route(a2a_ctx* ctx, int32_t* slots_out, int32_t* send_counts_out, v
 int a2a_route_noalloc(const int32_t* topk_idx, int num_tokens, int num_experts, int experts_per_token,
                       int32_t* slots_out, int32_t* send_counts_out, void* stream);
 
+/* The reference repository's second task (pmpp_v2/histogram_py): out[b] = number of bytes of
+ * data[0..n) equal to b, for b = 0..255 -- torch.bincount(data, minlength=256) on uint8 input
+ * (reference.py:6-19; native entry of its submission: submission_v1.py:20-113).  `data` is device
+ * memory (any alignment, any n >= 0), `out` 256 int64 in device memory, overwritten.  Needs no
+ * context; runs on the current device; enqueues a 2 KB memset and one kernel on `stream`. */
+int a2a_histogram256(const uint8_t* data, size_t n, int64_t* out, void* stream);
+
 /* Read the first error recorded by a kernel since the last a2a_status_clear.  Waits for
  * nothing on the caller's streams: reads what is there now. */
 int a2a_status(a2a_ctx* ctx, a2a_status_t* out);
