@@ -337,7 +337,7 @@ int do_combine(a2a_ctx* c, const float* w, void* y, cudaStream_t st) {
     if (!rows_aligned(y) || reinterpret_cast<uintptr_t>(w) % 4 != 0) return A2A_ERR_CONFIG;
     c->p.w = w;
     c->p.y = y;
-    const int nseg = (c->cfg.hidden_dim / 8 + 31) / 32;
+    const int nseg = (c->cfg.hidden_dim / 8 + 63) / 64;  // a warp per (token, 1 KB segment)
     const long long warps = (long long)c->cur_tokens * nseg;
     return launch(c, combine_fn(c), grid_for(c, (warps + kThreads / 32 - 1) / (kThreads / 32), 8), 0, st);
 }

@@ -388,13 +388,13 @@ __device__ __forceinline__ void expert_phase(const DevParams& p, const BlockSmem
 }
 
 // ---------------------------------------------------------------------------
-// Combine (pull).  A warp owns 32 consecutive 16-byte vectors (512 B) of one
+// Combine (pull).  A warp owns 64 consecutive 16-byte vectors (1 KB) of one
 // token's output.  Lane k < K looks up pair (t,k): expert, slot (known from routing,
 // so no metadata is fetched), weight, and waits (bounded) until the expert's rank has
 // published its outputs -- warp d of the grid is the watcher of rank d's flag, the
 // others wait on the local word; only then is the pair's slot read.  Pointer and weight are then broadcast by shuffles and
-// every lane pulls its 16 bytes of each of the K rows from the rank that holds them,
-// four loads in flight, accumulating float(row) * w in fp32 in k order.
+// every lane pulls its two 16-byte vectors of each of the K rows from the rank that holds
+// them, sixteen loads in flight, accumulating float(row) * w in fp32 in k order.
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void combine_phase(const DevParams& p, int cb, int ncb, bool own_watchers) {
@@ -402,7 +402,7 @@ __device__ __forceinline__ void combine_phase(const DevParams& p, int cb, int nc
     const int warp = cb * (kThreads / 32) + (threadIdx.x >> 5);
     const int nwarps = ncb * (kThreads / 32);
     const int K = p.K, nvec = p.H >> 3;
-    const int nseg = (nvec + 31) >> 5;
+    const int nseg = (nvec + 63) >> 6;  // a warp owns 64 consecutive vectors (1 KB) of one token's output
     for (int c = 0; c < p.chunks; ++c) {
     const uint32_t want = flag_value(p, c);
     const int ta = chunk_begin(p, c), tb = chunk_end(p, c);
@@ -415,7 +415,7 @@ __device__ __forceinline__ void combine_phase(const DevParams& p, int cb, int nc
     unsigned ready = 0u;  // ranks this lane has already seen ready for this chunk
     for (int item = warp; item < items; item += nwarps) {
         const int t = ta + item / nseg, seg = item % nseg;
-        const int v = seg * 32 + lane;
+        const int v0 = seg * 64 + lane, v1 = v0 + 32;
         unsigned long long my_row = 0ull;
         float my_w = 0.f;
         bool ok = true;
@@ -442,31 +442,42 @@ __device__ __forceinline__ void combine_phase(const DevParams& p, int cb, int nc
         }
         if (!__all_sync(0xffffffffu, ok)) return;  // timeout recorded; leave the remaining output untouched
         if (item == warp && c == 0) stamp(p, kStampExpertSeen);
-        float acc[8];
+        float acc[2][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int k0 = 0; k0 < K; k0 += 4) {
-            uint4 q[4];
-            float w[4];
-            bool have[4];
+        for (int i = 0; i < 8; ++i) acc[0][i] = acc[1][i] = 0.f;
+        // eight rows at a time, two 16-byte vectors of each per lane: sixteen loads are on their way over
+        // NVLink before the first is used (a pull is a round trip; what counts is how much is in flight)
+        for (int k0 = 0; k0 < K; k0 += 8) {
+            uint4 q[8][2];
+            float w[8];
+            bool have[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
                 const int k = (k0 + u < K) ? k0 + u : 0;
                 const unsigned long long row = __shfl_sync(0xffffffffu, my_row, k);
                 w[u] = __shfl_sync(0xffffffffu, my_w, k);
-                have[u] = (k0 + u < K) && row != 0ull && v < nvec;
-                if (have[u]) q[u] = ld_stream(reinterpret_cast<const uint4*>(row) + v);
+                have[u] = (k0 + u < K) && row != 0ull;
+                if (have[u] && v0 < nvec) q[u][0] = ld_stream(reinterpret_cast<const uint4*>(row) + v0);
+                if (have[u] && v1 < nvec) q[u][1] = ld_stream(reinterpret_cast<const uint4*>(row) + v1);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
                 if (have[u]) {
                     float f[8];
-                    unpack8<T>(q[u], f);
+                    if (v0 < nvec) {
+                        unpack8<T>(q[u][0], f);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[i] = fmaf(f[i], w[u], acc[i]);
+                        for (int i = 0; i < 8; ++i) acc[0][i] = fmaf(f[i], w[u], acc[0][i]);
+                    }
+                    if (v1 < nvec) {
+                        unpack8<T>(q[u][1], f);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[1][i] = fmaf(f[i], w[u], acc[1][i]);
+                    }
                 }
         }
-        if (v < nvec) st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v, pack8<T>(acc));
+        if (v0 < nvec) st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v0, pack8<T>(acc[0]));
+        if (v1 < nvec) st_stream(reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec + v1, pack8<T>(acc[1]));
     }
     }  // chunks
     __syncthreads();

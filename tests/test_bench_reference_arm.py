@@ -37,3 +37,13 @@ def test_reference_arm_under_torchrun_two_ranks_rank0_only_prints():
     assert len(lines) == 1
     d = json.loads(lines[0])
     assert d["n_gpus"] == 2 and d["config"]["world_size"] == 2 and "2 gloo process" in d["cpu_baseline"]["sample"]
+
+
+def test_reference_arm_of_the_histogram_workload():
+    """`--workload histogram --impl reference`: the reference's own operator call timed on the host cores."""
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload",
+                          "histogram", "--steps", "2", "--warmup", "1"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    d = _last_json(res.stdout)
+    assert d["impl"] == "reference" and d["metric"] == "histogram us" and d["dtype"] == "u8" and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] == "reference" and "bincount" in d["cpu_baseline"]["sample"]

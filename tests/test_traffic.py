@@ -28,3 +28,21 @@ def test_single_rank_hbm_bytes():
     b = traffic.hbm_bytes_single_rank(256, 8, 7168)
     assert b["recv_expert"] == 2 * 2048 * 14336
     assert b["dispatch_send"] == (256 + 2048) * 14336
+
+
+def test_wire_bytes_follow_payload_and_combine_mode():
+    """Algorithmic bytes never change; the wire carries one row per (token, rank) where the payload
+    (dispatch) or the expert-side reduction (combine) deduplicates."""
+    idx = [pkg.workload_input("c4", r, 8)[1].indices for r in range(8)]
+    H = 7168
+    direct = traffic.summarize(idx, 256, 8, H, "direct", "pull")
+    dedup_pull = traffic.summarize(idx, 256, 8, H, "dedup", "pull")
+    dedup_push = traffic.summarize(idx, 256, 8, H, "dedup", "push")
+    fp8_push = traffic.summarize(idx, 256, 8, H, "fp8", "push")
+    assert direct["algorithmic_bytes"] == dedup_pull["algorithmic_bytes"] == dedup_push["algorithmic_bytes"]
+    assert direct["wire_bytes"] == direct["algorithmic_bytes"]
+    b, bd = direct["busiest_rows"], direct["busiest_rows_dedup"]
+    assert dedup_pull["wire_bytes"] == (bd + b) * 2 * H
+    assert dedup_push["wire_bytes"] == 2 * bd * 2 * H
+    assert fp8_push["wire_bytes"] == bd * (H + 4 * (H // 128)) + bd * 2 * H
+    assert dedup_push["t_wire_us_nominal"] < dedup_pull["t_wire_us_nominal"] < direct["t_roof_us_nominal"]
