@@ -66,6 +66,16 @@ struct SendDesc {
 __device__ __forceinline__ unsigned dest_mask(const DevParams& p, int t) {
     unsigned m = 0;
     const int* row = p.idx + (size_t)t * p.K;
+    if ((p.K & 3) == 0 && (reinterpret_cast<uintptr_t>(p.idx) & 15) == 0) {  // the row is 16-byte aligned: vector loads
+        for (int k = 0; k < p.K; k += 4) {
+            const int4 e4 = __ldg(reinterpret_cast<const int4*>(row + k));
+            const int e[4] = {e4.x, e4.y, e4.z, e4.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (e[u] >= 0 && e[u] < p.E) m |= 1u << (e[u] / p.L);
+        }
+        return m;
+    }
     for (int k = 0; k < p.K; ++k) {
         const int e = __ldg(row + k);
         if (e >= 0 && e < p.E) m |= 1u << (e / p.L);
@@ -178,11 +188,11 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
     unsigned short* list = m.list;
     const int per = m.per;
     __shared__ int s_cnt[A2A_MAX_WORLD];
-    build_send_lists(p, m, sb, ns, s_cnt);
-    if (tid == 0) {
+    if (tid == 0) {  // before the lists: thread 0 can issue its first loads the moment they are built
         for (int s = 0; s < kStages; ++s) mbar_init(smem_addr(bars + s), 1);
         mbar_fence_init();
     }
+    build_send_lists(p, m, sb, ns, s_cnt);
     __syncthreads();
     stamp(p, kStampSetup + 0);
     if (tid != 0) {
