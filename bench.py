@@ -485,7 +485,9 @@ def main():
         from gpu_mode_kernels_b200 import trace as tracing
 
         ctx.trace_enable(True)
-        if ws > 1:
+        sync_all()  # the hosts level; then two device-side rendezvous back to back: when the second one lets go,
+        if ws > 1:  # every rank's forward is already queued behind it, so the ranks start within a microsecond or two
+            ctx.barrier()
             ctx.barrier()
         ctx.forward(rd.x, rd.indices, rd.weights, y)
         stamps = ctx.trace_read()

@@ -174,6 +174,32 @@ __device__ __forceinline__ void build_send_lists(const DevParams& p, const Sende
     }
 }
 
+// A sender thread's destinations whose last store has been issued but not yet waited for, oldest
+// first.  Bulk groups complete in order, so destination d (last group g_d) is through once at most
+// (groups committed since g_d) groups are pending.  Nothing is waited for at a destination boundary:
+// a destination is booked `kArrivalLag` stores later, or at the end -- with one row per destination
+// (small batches) all rows leave back to back and one wait at the end covers them.
+struct PendingDests {
+    int d[A2A_MAX_WORLD];
+    long long g[A2A_MAX_WORLD];
+    int head = 0, tail = 0;
+    __device__ __forceinline__ bool empty() const { return head == tail; }
+    __device__ __forceinline__ void push(int dest, long long group) {
+        d[tail % A2A_MAX_WORLD] = dest;
+        g[tail % A2A_MAX_WORLD] = group;
+        ++tail;
+    }
+    // Book every destination that is at least `lag` groups old (lag 0: all of them); `now` = groups committed so far.
+    template <typename Arrive>
+    __device__ __forceinline__ void drain(long long now, int lag, Arrive arrive) {
+        while (head != tail && now - 1 - g[head % A2A_MAX_WORLD] >= lag) {
+            bulk_wait_done((int)min(now - 1 - g[head % A2A_MAX_WORLD], 5LL));
+            arrive(d[head % A2A_MAX_WORLD]);
+            ++head;
+        }
+    }
+};
+
 // Sender block `sb` of `ns`, 16-bit payload: all threads build the block's token lists; then
 // thread 0 drives the copy engine (rows go HBM -> shared-memory ring -> peer without touching a
 // register) while, if `watch_kind` >= 0, warps 1.. watch the peers' flags of that kind (they
@@ -215,7 +241,10 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
         if (mine == 0) arrive(d);  // nothing of ours goes there
         total += (long long)mine * pieces;
     }
-    constexpr int kLook = kStages - 2;  // loads issued ahead of the store that follows them
+    // A bulk store to a peer holds its stage until the peer has acknowledged the write (measured: with two
+    // store stages a block moves 28 KB per ~1.5 us round trip whatever the link could take), local loads
+    // complete in about a microsecond: two loads ahead, four stores in flight.
+    constexpr int kLook = 2;
     int g_step = 1, g_i = 0, g_piece = 0;  // generator of the next piece to load
     auto skip_empty = [&] {
         while (g_step < p.ws) {
@@ -227,7 +256,7 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
         }
     };
     skip_empty();
-    int pend_d = -1, pend_age = 0;
+    PendingDests pending;
     bool failed = false;
     for (long long q = 0; q < total + kLook && !failed; ++q) {
         if (q < total) {
@@ -274,82 +303,67 @@ __device__ __forceinline__ void sender_role(const DevParams& p, uint8_t* smem, i
             bulk_store(reinterpret_cast<void*>(desc[st].dst), smem_addr(ring + (size_t)st * kStageBytes), desc[st].bytes);
             bulk_commit();
             if (it == 0) stamp(p, kStampSetup + 2);
-            if (pend_d >= 0 && ++pend_age >= kArrivalLag) {  // that many groups later the old one has been acknowledged, or nearly
-                bulk_wait_done(pend_age);
-                arrive(pend_d);
-                pend_d = -1;
-            }
-            if (desc[st].dest_done >= 0) {
-                if (pend_d >= 0) {
-                    bulk_wait_done(pend_age);
-                    arrive(pend_d);
-                }
-                pend_d = desc[st].dest_done;
-                pend_age = 0;
-            }
+            if (desc[st].dest_done >= 0) pending.push(desc[st].dest_done, it);  // group `it` was the destination's last
+            pending.drain(it + 1, kArrivalLag, arrive);
         }
     }
     bulk_wait_done(0);  // nothing of ours is in flight when the block moves on
-    if (pend_d >= 0 && !failed) arrive(pend_d);
+    if (!failed)
+        while (!pending.empty()) pending.drain(1LL << 40, 0, arrive);
 }
 
-// Sender block `sb` of `ns`, FP8 payload: a warp per wire row.  The warp reads the row with
-// 16-byte loads (eight in flight per lane), quantises it to e4m3 with one fp32 scale per 128
-// values into its own stage of the ring, and lane 0 hands the finished wire row to the copy
-// engine.  Dedicated watcher blocks poll the flags (every warp here is busy).
-constexpr int kWarpStageBytes = kStages * kStageBytes / (kThreads / 32);  // 12 KB per warp
+// Sender block `sb` of `ns`, FP8 payload: the whole block quantises one wire row at a time (the
+// arithmetic -- an IEEE division per value -- is the cost here, so all eight warps share a row):
+// 16-byte loads, amax over the 16 lanes of a 128-value block, e4m3 bytes and fp32 scales into one of
+// eight 12 KB stages of the ring, then thread 0 hands the finished wire row to the copy engine and
+// the block goes on to the next row while up to seven stores are still on their way.
+constexpr int kFp8Stages = 8;
+constexpr int kWarpStageBytes = kStages * kStageBytes / kFp8Stages;  // 12 KB: the largest FP8 wire row
 
 template <typename T>
 __device__ __forceinline__ void sender_role_fp8(const DevParams& p, uint8_t* smem, int sb, int ns) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const SenderSmem m = carve_sender(p, smem, ns);
     __shared__ int s_cnt[A2A_MAX_WORLD];
-    __shared__ int s_done[A2A_MAX_WORLD];
     build_send_lists(p, m, sb, ns, s_cnt);
-    if (tid < A2A_MAX_WORLD) s_done[tid] = 0;
     __syncthreads();
+    stamp(p, kStampSetup + 0);
     const uint32_t expected = (uint32_t)(ns + p.routers);
-    constexpr int kWarps = kThreads / 32;
-    uint8_t* stage = m.ring + (size_t)warp * kWarpStageBytes;
-    const int nvec = p.H >> 3;
-    // lane 0: a warp whose stores to d are complete books it; the block's last warp draws the ticket
-    auto warp_arrive = [&](int d) {
-        fence_async_global();
-        __threadfence();
-        if (atomicAdd(&s_done[d], 1) == kWarps - 1) {
-            __threadfence();
-            arrive_dest(p, d, expected);
-            stamp_by(p, kStampDestDone + (d - p.rank + p.ws) % p.ws, true);
-        }
+    auto arrive = [&](int d) {  // thread 0 only
+        arrive_dest(p, d, expected);
+        stamp(p, kStampDestDone + (d - p.rank + p.ws) % p.ws);
     };
-    int pend_d = -1, pend_age = 0;
-    bool used = false;
+    const int nvec = p.H >> 3;
+    PendingDests pending;  // thread 0's bookkeeping, as in the 16-bit sender
+    long long q = 0;       // rows this block has sent so far
     for (int i = 1; i < p.ws; ++i) {
         const int d = (p.rank + i) % p.ws;
         const int mine = s_cnt[d] > sb ? (s_cnt[d] - sb + ns - 1) / ns : 0;
-        bool any = false;
-        for (int g = warp; g < mine; g += kWarps) {
+        if (mine == 0) {
+            if (tid == 0) arrive(d);  // nothing of ours goes there
+            continue;
+        }
+        for (int g = 0; g < mine; ++g, ++q) {
             const int n = sb + g * ns;
             const int t = m.list[d * m.per + g];
-            if (used) {
-                if (lane == 0) bulk_wait_read<0>();  // the previous store has read this warp's stage
-                __syncwarp();
-            }
+            uint8_t* stage = m.ring + (size_t)(q % kFp8Stages) * kWarpStageBytes;
+            if (tid == 0 && q >= kFp8Stages) bulk_wait_read<kFp8Stages - 1>();  // the store that used this stage has read it
+            __syncthreads();
             const uint4* src = reinterpret_cast<const uint4*>(p.x) + (size_t)t * nvec;
-            for (int v0 = 0; v0 < nvec; v0 += 256) {
-                uint4 q[8];
+            for (int v0 = 0; v0 < nvec; v0 += 4 * kThreads) {
+                uint4 qv[4];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int v = v0 + u * 32 + lane;
-                    if (v < nvec) q[u] = ld_input(src + v);
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * kThreads + tid;
+                    if (v < nvec) qv[u] = ld_input(src + v);
                 }
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int v = v0 + u * 32 + lane;  // nvec % 16 == 0: the 16 lanes of a scale block are all in or all out
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * kThreads + tid;  // nvec % 16 == 0: the 16 lanes of a scale block are all in or all out
                     float f[8];
                     float amax = 0.f;
                     if (v < nvec) {
-                        unpack8<T>(q[u], f);
+                        unpack8<T>(qv[u], f);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
                     }
@@ -364,38 +378,21 @@ __device__ __forceinline__ void sender_role_fp8(const DevParams& p, uint8_t* sme
                     }
                 }
             }
-            fence_async_smem();  // the warp's ordinary stores to its stage, before the copy engine reads it
-            __syncwarp();
-            if (lane == 0) {
+            fence_async_smem();  // every thread's ordinary stores to the stage, before the copy engine reads it
+            __syncthreads();
+            if (tid == 0) {
                 uint8_t* dst = p.peer[d] + p.off_stage + ((size_t)p.rank * p.T_max + n) * p.stage_row_bytes;
                 bulk_store(dst, smem_addr(stage), (uint32_t)p.stage_row_bytes);
                 bulk_commit();
-                if (pend_d >= 0 && ++pend_age >= kArrivalLag) {
-                    bulk_wait_done(pend_age);
-                    warp_arrive(pend_d);
-                    pend_d = -1;
-                }
-            }
-            used = true;
-            any = true;
-        }
-        if (lane == 0) {
-            if (pend_d >= 0 && any) {  // an older destination is still pending: its stores precede this one's
-                bulk_wait_done(pend_age);
-                warp_arrive(pend_d);
-                pend_d = -1;
-            }
-            if (any) {
-                pend_d = d;
-                pend_age = 0;
-            } else {
-                warp_arrive(d);  // nothing of this warp goes there
+                if (q == 0) stamp(p, kStampSetup + 2);
+                if (g == mine - 1) pending.push(d, q);  // the block's last row for d
+                pending.drain(q + 1, kArrivalLag, arrive);
             }
         }
     }
-    if (lane == 0) {
+    if (tid == 0) {
         bulk_wait_done(0);
-        if (pend_d >= 0) warp_arrive(pend_d);
+        while (!pending.empty()) pending.drain(1LL << 40, 0, arrive);
     }
 }
 
@@ -731,7 +728,7 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
 
 // ---------------------------------------------------------------------------
 // Combine at home, PUSH: y[t] = T(sum over the ranks d holding experts of t, ascending,
-// of float(partial[d][t])).  Block `cb` of `ncb`; a warp per (token, 2 KB chunk).
+// of float(partial[d][t])).  Block `cb` of `ncb`; a warp per (token, 1 KB segment).
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, int ncb) {
@@ -773,59 +770,49 @@ __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, in
     if (!s_ok) return;  // timeout recorded; y is left untouched
     stamp(p, kStampExpertSeen);
     const uint4* ret = reinterpret_cast<const uint4*>(p.peer[p.rank] + p.off_ret);
-    const long long items = (long long)p.T * nchunk;
+    // a warp per (token, 1 KB segment): two vectors per lane of EVERY contributing rank's partial row
+    // are requested before the first is used (up to sixteen loads in flight), then added in rank order
+    const int nseg = (nvec + 63) >> 6;
+    const long long items = (long long)p.T * nseg;
     const int cw = cb * (kThreads / 32) + (tid >> 5), ncw = ncb * (kThreads / 32);
     for (long long it = cw; it < items; it += ncw) {
-        const int t = (int)(it / nchunk), v0 = (int)(it - (long long)t * nchunk) * 128;
+        const int t = (int)(it / nseg);
+        const int v0 = (int)(it - (long long)t * nseg) * 64 + lane, v1 = v0 + 32;
         unsigned bit = 0u;
         if (lane < K) {
             const int e = __ldg(p.idx + (size_t)t * K + lane);
             if (e >= 0 && e < p.E) bit = 1u << (e / p.L);
         }
-        unsigned mask = __reduce_or_sync(0xffffffffu, bit);
-        float acc[4][8];
+        const unsigned mask = __reduce_or_sync(0xffffffffu, bit);
+        uint4 q[A2A_MAX_WORLD][2];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int d = 0; d < A2A_MAX_WORLD; ++d)
+            if ((mask >> d) & 1u) {
+                const uint4* row = ret + ((size_t)d * p.T_max + t) * nvec;
+                if (v0 < nvec) q[d][0] = ld_stream(row + v0);
+                if (v1 < nvec) q[d][1] = ld_stream(row + v1);
+            }
+        float acc[2][8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
-        while (mask) {  // two ranks' partial rows in flight at a time, added in rank order
-            const int d0 = __ffs(mask) - 1;
-            mask &= mask - 1;
-            const int d1 = mask ? __ffs(mask) - 1 : -1;
-            mask &= mask - 1;
-            const uint4* row0 = ret + ((size_t)d0 * p.T_max + t) * nvec;
-            const uint4* row1 = ret + ((size_t)(d1 < 0 ? d0 : d1) * p.T_max + t) * nvec;
-            uint4 q0[4], q1[4];
+        for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int v = v0 + u * 32 + lane;
-                if (v < nvec) {
-                    q0[u] = ld_stream(row0 + v);
-                    if (d1 >= 0) q1[u] = ld_stream(row1 + v);
+        for (int d = 0; d < A2A_MAX_WORLD; ++d)
+            if ((mask >> d) & 1u) {
+                float f[8];
+                if (v0 < nvec) {
+                    unpack8<T>(q[d][0], f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[0][e] += f[e];
+                }
+                if (v1 < nvec) {
+                    unpack8<T>(q[d][1], f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[1][e] += f[e];
                 }
             }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int v = v0 + u * 32 + lane;
-                if (v < nvec) {
-                    float f[8];
-                    unpack8<T>(q0[u], f);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
-                    if (d1 >= 0) {
-                        unpack8<T>(q1[u], f);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
-                    }
-                }
-            }
-        }
         uint4* y = reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int v = v0 + u * 32 + lane;
-            if (v < nvec) st_stream(y + v, pack8<T>(acc[u]));
-        }
+        if (v0 < nvec) st_stream(y + v0, pack8<T>(acc[0]));
+        if (v1 < nvec) st_stream(y + v1, pack8<T>(acc[1]));
     }
     __syncthreads();
     stamp(p, kStampCombineDone);
