@@ -485,9 +485,13 @@ def main():
         from gpu_mode_kernels_b200 import trace as tracing
 
         ctx.trace_enable(True)
-        sync_all()  # the hosts level; then two device-side rendezvous back to back: when the second one lets go,
-        if ws > 1:  # every rank's forward is already queued behind it, so the ranks start within a microsecond or two
-            ctx.barrier()
+        sync_all()
+        # Two L2 flushes (~70 us each) keep the GPU busy while the host queues the rendezvous and the forward
+        # behind them: when the rendezvous lets go, every rank's forward is already waiting in its stream, so
+        # the ranks start within a microsecond or two of each other -- as they do in the timed loop.
+        flush.fill_(0)
+        flush.fill_(1)
+        if ws > 1:
             ctx.barrier()
         ctx.forward(rd.x, rd.indices, rd.weights, y)
         stamps = ctx.trace_read()

@@ -728,7 +728,7 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
 
 // ---------------------------------------------------------------------------
 // Combine at home, PUSH: y[t] = T(sum over the ranks d holding experts of t, ascending,
-// of float(partial[d][t])).  Block `cb` of `ncb`; a warp per (token, 1 KB segment).
+// of float(partial[d][t])).  Block `cb` of `ncb`; a warp per (token, 2 KB chunk).
 // ---------------------------------------------------------------------------
 template <typename T>
 __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, int ncb) {
@@ -770,49 +770,58 @@ __device__ __forceinline__ void combine_home_role(const DevParams& p, int cb, in
     if (!s_ok) return;  // timeout recorded; y is left untouched
     stamp(p, kStampExpertSeen);
     const uint4* ret = reinterpret_cast<const uint4*>(p.peer[p.rank] + p.off_ret);
-    // a warp per (token, 1 KB segment): two vectors per lane of EVERY contributing rank's partial row
-    // are requested before the first is used (up to sixteen loads in flight), then added in rank order
-    const int nseg = (nvec + 63) >> 6;
-    const long long items = (long long)p.T * nseg;
+    // a warp per (token, 2 KB chunk): four vectors per lane of up to four contributing ranks' partial rows
+    // are requested before the first is used (sixteen loads in flight), ranks 0-3 then 4-7, added in rank order
+    const long long items = (long long)p.T * nchunk;
     const int cw = cb * (kThreads / 32) + (tid >> 5), ncw = ncb * (kThreads / 32);
     for (long long it = cw; it < items; it += ncw) {
-        const int t = (int)(it / nseg);
-        const int v0 = (int)(it - (long long)t * nseg) * 64 + lane, v1 = v0 + 32;
+        const int t = (int)(it / nchunk), v0 = (int)(it - (long long)t * nchunk) * 128;
         unsigned bit = 0u;
         if (lane < K) {
             const int e = __ldg(p.idx + (size_t)t * K + lane);
             if (e >= 0 && e < p.E) bit = 1u << (e / p.L);
         }
         const unsigned mask = __reduce_or_sync(0xffffffffu, bit);
-        uint4 q[A2A_MAX_WORLD][2];
+        float acc[4][8];
 #pragma unroll
-        for (int d = 0; d < A2A_MAX_WORLD; ++d)
-            if ((mask >> d) & 1u) {
-                const uint4* row = ret + ((size_t)d * p.T_max + t) * nvec;
-                if (v0 < nvec) q[d][0] = ld_stream(row + v0);
-                if (v1 < nvec) q[d][1] = ld_stream(row + v1);
-            }
-        float acc[2][8];
+        for (int u = 0; u < 4; ++u)
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[0][e] = acc[1][e] = 0.f;
+            for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
 #pragma unroll
-        for (int d = 0; d < A2A_MAX_WORLD; ++d)
-            if ((mask >> d) & 1u) {
-                float f[8];
-                if (v0 < nvec) {
-                    unpack8<T>(q[d][0], f);
+        for (int g = 0; g < A2A_MAX_WORLD; g += 4) {
+            if (((mask >> g) & 0xfu) == 0u) continue;
+            uint4 q[4][4];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[0][e] += f[e];
+            for (int j = 0; j < 4; ++j)
+                if ((mask >> (g + j)) & 1u) {
+                    const uint4* row = ret + ((size_t)(g + j) * p.T_max + t) * nvec;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = v0 + u * 32 + lane;
+                        if (v < nvec) q[j][u] = ld_stream(row + v);
+                    }
                 }
-                if (v1 < nvec) {
-                    unpack8<T>(q[d][1], f);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[1][e] += f[e];
+            for (int j = 0; j < 4; ++j)
+                if ((mask >> (g + j)) & 1u) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = v0 + u * 32 + lane;
+                        if (v < nvec) {
+                            float f[8];
+                            unpack8<T>(q[j][u], f);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[u][e] += f[e];
+                        }
+                    }
                 }
-            }
+        }
         uint4* y = reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec;
-        if (v0 < nvec) st_stream(y + v0, pack8<T>(acc[0]));
-        if (v1 < nvec) st_stream(y + v1, pack8<T>(acc[1]));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * 32 + lane;
+            if (v < nvec) st_stream(y + v, pack8<T>(acc[u]));
+        }
     }
     __syncthreads();
     stamp(p, kStampCombineDone);
