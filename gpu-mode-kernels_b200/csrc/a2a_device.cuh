@@ -126,14 +126,6 @@ __device__ __forceinline__ void stamp_by(const DevParams& p, int which, bool ele
     if (p.trace != nullptr && elected) p.trace[(size_t)blockIdx.x * kNumStamps + which] = clock64();
 }
 
-// Named barriers (ids 1..15; 0 is __syncthreads): `count` threads take part, arrivals do not wait.
-__device__ __forceinline__ void named_bar_arrive(int id, int count) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 // Value stamp (not a time): e.g. the role of the block.
 __device__ __forceinline__ void stamp_value(const DevParams& p, int which, long long v) {
     if (p.trace != nullptr && threadIdx.x == 0) p.trace[(size_t)blockIdx.x * kNumStamps + which] = v;

@@ -18,9 +18,11 @@
 //   experts  (all other blocks) take the sources in arrival order (own rank first, then
 //            rank-1, rank-2, ...).  Per wire row: read it once, write each slab row it
 //            stands for (the dispatch output) with the placeholder expert op applied, and
-//            -- PUSH combine -- accumulate w[t,k] * row in fp32 and store ONE partial row
-//            per (token, this rank) into the home rank's return buffer over NVLink.  The
-//            block that finishes a source last publishes the expert flag to that source.
+//            -- PUSH combine -- accumulate w[t,k] * row in fp32 and return ONE partial row
+//            per (token, this rank) to the home rank's return buffer over NVLink (packed in
+//            shared memory and bulk-stored, like the senders' rows).  Inside a block warp 0
+//            polls the sources' flags, warps 2-7 work, warp 1 draws the block's ticket per
+//            source; the last ticket publishes the expert flag to that source.
 //   watchers (spare warps of sender blocks 0 and 1) poll the peers' flags at system scope
 //            and hand them to the rest of the GPU through local words.
 //   combine  (every block, once its role is done) PUSH: y[t] = sum over the ranks that hold
@@ -576,59 +578,68 @@ __device__ __forceinline__ void load_wire_chunk(const DevParams& p, bool own, co
 // ---------------------------------------------------------------------------
 // Expert block `xb` of `nxb`.  Sources are taken in arrival order (own rank first, then
 // rank-1, rank-2, ...).  Inside a block the warps have fixed jobs so that no source ever waits
-// for the bookkeeping of the one before it:
-//   warp 0 (lane 0)  poller: waits for the sources' dispatch flags in order, reads each source's
-//                    row count and raises a shared-memory word the workers spin on;
-//   warp 1           completer: joins the workers of source i at named barrier 1+i, then fences
-//                    (gpu scope; this is where the stores to the home rank are waited for) and draws
-//                    the block's ticket for that source -- the last ticket publishes the expert flag;
-//   warps 2..7       workers: every worker warp of every expert block takes (wire row, 2 KB chunk)
-//                    items round-robin, continuing across sources where the previous one left off;
-//                    having stored its share of source i a warp ARRIVES at barrier 1+i without waiting
-//                    and goes on to source i+1.
+// for the bookkeeping of another:
+//   warp 0  pollers: lane i waits for the dispatch flag of source position i, reads that source's
+//           row count and raises a shared-memory word the workers spin on -- all sources at once,
+//           so a batch whose rows are all there costs one flag latency, not one per source;
+//   warp 1  completers: lane i waits until every worker warp has booked source i in a shared-memory
+//           counter, fences (gpu scope; this is where the stores to the home rank are waited for) and
+//           draws the block's ticket for that source -- the last ticket publishes the expert flag;
+//   warps 2..7  workers: every worker warp of every expert block takes (wire row, 2 KB chunk) items
+//           round-robin, continuing across sources where the previous one left off; having stored
+//           its share of source i a warp fences at block scope, books the source and goes on to
+//           source i+1 without waiting for anything.  PUSH: the partial row of a REMOTE token goes
+//           home through the copy engine -- packed into one of the warp's two 2 KB shared-memory
+//           slots and bulk-stored -- so that the back-pressure of the link never sits in the load /
+//           store path of the SM in front of the slab stores and the next item's loads; such a source
+//           is booked one source later (by then its bulk stores have long completed), the last at once.
 // ---------------------------------------------------------------------------
 constexpr int kExpertWorkers = kThreads / 32 - 2;
-constexpr int kExpertBarThreads = (kExpertWorkers + 1) * 32;  // workers + completer
+
+constexpr int kReturnSlotBytes = 2048;  // one 2 KB chunk of a partial row, two slots per worker warp
 
 template <typename T, int PAYLOAD, bool PUSH>
-__device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb) {
+__device__ __forceinline__ void expert_role(const DevParams& p, uint8_t* smem, int xb, int nxb) {
     __shared__ volatile int s_seen[A2A_MAX_WORLD];  // 0 waiting, 1 rows of source position i are here, -1 gave up
     __shared__ volatile int s_rows[A2A_MAX_WORLD];  // wire rows of source position i
+    __shared__ int s_done[A2A_MAX_WORLD];           // worker warps that are through with source position i
+    __shared__ volatile int s_dead;                 // a wait gave up: nothing further is published
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int K = p.K, nvec = p.H >> 3;
     const int nchunk = (nvec + 127) >> 7;
     const uint32_t want = flag_value(p, 0);
     uint8_t* self = p.peer[p.rank];
-    if (tid < A2A_MAX_WORLD) s_seen[tid] = 0;
+    if (tid < A2A_MAX_WORLD) {
+        s_seen[tid] = 0;
+        s_done[tid] = 0;
+    }
+    if (tid == 0) s_dead = 0;
     __syncthreads();
     if (warp == 0) {
-        if (lane == 0) {
-            bool ok = true;
-            for (int i = 0; i < p.ws; ++i) {
-                const int s = (p.rank - i + p.ws) % p.ws;
-                ok = ok && wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s);
-                int n_s = 0;
-                if (ok) {
-                    n_s = ld_stream(reinterpret_cast<const int*>(self + p.off_hdr) + s * 8);
-                    if (n_s < 0 || n_s > p.T_max) {
-                        record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, n_s);
-                        n_s = 0;
-                    }
+        if (lane < p.ws) {
+            const int i = lane, s = (p.rank - i + p.ws) % p.ws;
+            const bool ok = wait_flag_gpu(seen_ptr(p, kFlagDispatch, s), want, p, kPhaseRecv, s);
+            int n_s = 0;
+            if (ok) {
+                n_s = ld_stream(reinterpret_cast<const int*>(self + p.off_hdr) + s * 8);
+                if (n_s < 0 || n_s > p.T_max) {
+                    record_error(p.status, A2A_ERR_CAPACITY, p.rank, s, kPhaseExpert, p.epoch, n_s);
+                    n_s = 0;
                 }
-                s_rows[i] = n_s;
-                __threadfence_block();
-                s_seen[i] = ok ? 1 : -1;  // after a timeout every later source is given up as well
-                stamp_by(p, kStampSourceSeen + i, ok);
             }
+            s_rows[i] = n_s;
+            __threadfence_block();
+            s_seen[i] = ok ? 1 : -1;
+            stamp_by(p, kStampSourceSeen + i, ok);
         }
         return;
     }
     if (warp == 1) {
-        for (int i = 0; i < p.ws; ++i) {
-            named_bar_sync(1 + i, kExpertBarThreads);  // every worker warp has stored its share of source i
-            if (lane == 0 && s_seen[i] == 1) {
-                const int s = (p.rank - i + p.ws) % p.ws;
-                __threadfence();
+        if (lane < p.ws) {
+            const int i = lane, s = (p.rank - i + p.ws) % p.ws;
+            while (*reinterpret_cast<volatile int*>(&s_done[i]) < kExpertWorkers) __nanosleep(40);  // bounded by the pollers' bounded waits
+            if (!s_dead) {
+                __threadfence();  // cumulative: the workers' stores, ordered before their bookings at block scope
                 uint32_t* ticket = p.ptickets + kPipeTicketSource * A2A_MAX_WORLD + s;
                 if (atomicAdd(ticket, 1u) == (uint32_t)nxb - 1u) {
                     *ticket = 0;
@@ -641,7 +652,6 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
                 }
                 stamp_by(p, kStampSourceDone + i, true);
             }
-            __syncwarp();
         }
         return;
     }
@@ -649,13 +659,27 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
     const int nxw = nxb * kExpertWorkers;
     const float scale = (float)(1 + p.rank);
     uint4* rows = reinterpret_cast<uint4*>(self + p.off_rows);
+    uint8_t* slots = smem + (size_t)(warp - 2) * 2 * kReturnSlotBytes;  // this warp's two return slots
+    auto book = [&](int i) {  // lane 0: this warp is through with source position i
+        __threadfence_block();
+        atomicAdd(&s_done[i], 1);
+    };
     long long cursor = 0;
+    int pending = -1;         // lane 0: a source whose bulk stores are still to be waited for
+    long long groups = 0;     // lane 0: bulk groups this warp has committed so far
+    long long pending_groups = 0;
     for (int i = 0; i < p.ws; ++i) {
         int seen;
         while ((seen = s_seen[i]) == 0) __nanosleep(40);  // bounded by the poller's own bounded wait
         if (seen < 0) {
-            // nothing further is processed or published; the completer is still owed this warp's arrivals
-            for (int j = i; j < p.ws; ++j) named_bar_arrive(1 + j, kExpertBarThreads);
+            // nothing further is processed or published; the completers are still owed this warp's bookings
+            if (lane == 0) {
+                s_dead = 1;
+                __threadfence_block();
+                bulk_wait_done(0);
+                if (pending >= 0) atomicAdd(&s_done[pending], 1);
+                for (int j = i; j < p.ws; ++j) atomicAdd(&s_done[j], 1);
+            }
             return;
         }
         const int s = (p.rank - i + p.ws) % p.ws;
@@ -664,6 +688,7 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
         const unsigned* rec_ent = reinterpret_cast<const unsigned*>(self + p.off_rec_ent) + (size_t)s * p.T_max * K;
         const float* rec_w = reinterpret_cast<const float*>(self + p.off_rec_w) + (size_t)s * p.T_max * K;
         const bool own = (s == p.rank);
+        const bool via_engine = PUSH && !own;  // the home rank is a peer: return through the copy engine
         const long long items = (long long)n_s * nchunk;
         for (long long it = (xw - cursor % nxw + nxw) % nxw; it < items; it += nxw) {
             const int n = (int)(it / nchunk), v0 = (int)(it - (long long)n * nchunk) * 128;
@@ -709,20 +734,58 @@ __device__ __forceinline__ void expert_role(const DevParams& p, int xb, int nxb)
                     }
                 }
             }
-            if (PUSH) {
-                // one rank: the partial row IS the token's output -- no return buffer, no combine pass
+            if (PUSH && !via_engine) {
+                // one rank: the partial row IS the token's output -- no return buffer, no combine pass;
+                // own tokens of several ranks: the return buffer is local memory
                 uint4* home = p.ws == 1 ? reinterpret_cast<uint4*>(p.y) + (size_t)t * nvec
-                                        : reinterpret_cast<uint4*>(p.peer[s] + p.off_ret) + ((size_t)p.rank * p.T_max + t) * nvec;
+                                        : reinterpret_cast<uint4*>(self + p.off_ret) + ((size_t)p.rank * p.T_max + t) * nvec;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int v = v0 + u * 32 + lane;
                     if (v < nvec) st_stream(home + v, pack8<T>(acc[u]));
                 }
             }
+            if (via_engine) {
+                uint8_t* slot = slots + (size_t)(groups & 1) * kReturnSlotBytes;  // `groups` is warp-uniform: every lane counts
+                if (groups >= 2) {
+                    if (lane == 0) bulk_wait_read<1>();  // the store that used this slot two items ago has read it
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * 32 + lane;
+                    if (v < nvec) reinterpret_cast<uint4*>(slot)[u * 32 + lane] = pack8<T>(acc[u]);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    uint8_t* home = p.peer[s] + p.off_ret + (((size_t)p.rank * p.T_max + t) * nvec + v0) * 16;
+                    bulk_store(home, smem_addr(slot), (uint32_t)(min(128, nvec - v0) * 16));
+                    bulk_commit();
+                }
+                ++groups;
+            }
         }
         cursor += items;
-        __syncwarp();
-        named_bar_arrive(1 + i, kExpertBarThreads);
+        __syncwarp();  // every lane's stores of this source precede lane 0's fence and booking
+        if (lane == 0) {
+            if (pending >= 0) {  // the source before: its bulk stores are at least this source's items old
+                bulk_wait_done((int)min(groups - pending_groups, 5LL));
+                fence_async_global();
+                book(pending);
+                pending = -1;
+            }
+            if (via_engine && i + 1 < p.ws) {
+                pending = i;
+                pending_groups = groups;
+            } else {
+                if (via_engine) {  // the last source: nothing comes after it to hide the wait behind
+                    bulk_wait_done(0);
+                    fence_async_global();
+                }
+                book(i);
+            }
+        }
     }
 }
 
@@ -875,7 +938,7 @@ __global__ void __launch_bounds__(kThreads, 2) pipe_forward_kernel(const __grid_
             stamp(p, kStampSent);
         }
         stamp_value(p, kStampRole, xb < p.ws * p.routers ? (kRoleExpert | kRoleRouter) : kRoleExpert);
-        expert_role<T, PAYLOAD, PUSH>(p, xb, nxb);
+        expert_role<T, PAYLOAD, PUSH>(p, a2a_pipe_smem, xb, nxb);
     }
     __syncthreads();
     stamp(p, kStampExpertDone);
@@ -907,7 +970,7 @@ __global__ void __launch_bounds__(kThreads, 2) pipe_role_kernel(const __grid_con
         stamp(p, kStampSent);
     } else if (ROLE == 1) {
         if (b == 0) watcher_role(p, kFlagDispatch, kPhaseRecv, (int)(threadIdx.x >> 5));
-        else expert_role<T, PAYLOAD, PUSH>(p, b - 1, G - 1);
+        else expert_role<T, PAYLOAD, PUSH>(p, a2a_pipe_smem, b - 1, G - 1);
         stamp(p, kStampExpertDone);
     } else {
         if (b == 0) {
