@@ -141,6 +141,22 @@ def test_fp8_edge_shapes(combine):
         world.close()
 
 
+@pytest.mark.parametrize("combine", COMBINES)
+def test_a_rank_without_tokens(combine):
+    """One rank of three brings no tokens at all to a call (its experts still serve the others)."""
+    ws, E, K, H, T = 3, 12, 3, 256, 40
+    datas = [pkg.generate_input(E, K, H, T, seed=8, rank=r, world_size=ws, ragged=True) for r in range(ws)]
+    cfg = datas[0][0]
+    rds = [d[1] for d in datas]
+    rds[1].num_tokens = 0
+    rds[1].x, rds[1].indices, rds[1].weights = rds[1].x[:0], rds[1].indices[:0], rds[1].weights[:0]
+    world, out = run_case(cfg, ws, rds, combine)
+    try:
+        assert out[1].shape == (0, H)
+    finally:
+        world.close()
+
+
 @pytest.mark.parametrize("spec", pkg.REFERENCE_TESTS + pkg.REFERENCE_BENCHMARKS,
                          ids=lambda s: "E{}_K{}_H{}_T{}".format(*s[:4]))
 def test_reference_task_shapes_fp16(spec):
