@@ -52,6 +52,9 @@ def parse_args():
     ap.add_argument("--no-verify", action="store_true",
                     help="skip the check of one forward of every rank (dispatch digests and outputs) against the CPU checker")
     ap.add_argument("--skip-link-probe", action="store_true")
+    ap.add_argument("--no-l2-flush", action="store_true",
+                    help="diagnostic only: leave the L2 warm between steps (such a number breaks the timing rules and "
+                         "is labelled so in config.l2)")
     ap.add_argument("--trace", default=None, help="write the merged in-kernel trace of one forward (chrome JSON) here")
     ap.add_argument("--per-phase-launches", action="store_true",
                     help="phased schedule: run the forward as one kernel per phase instead of one cooperative launch")
@@ -314,7 +317,8 @@ def main():
 
     def timed_loop(step_fn, steps, warmup):
         for i in range(warmup):
-            flush.fill_(i & 1)
+            if not args.no_l2_flush:
+                flush.fill_(i & 1)
             if ws > 1:
                 ctx.barrier()
             step_fn()
@@ -322,7 +326,8 @@ def main():
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         l0 = ctx.launches
         for i in range(steps):
-            flush.fill_(i & 1)
+            if not args.no_l2_flush:
+                flush.fill_(i & 1)
             if ws > 1:
                 ctx.barrier()
             ev[i][0].record(stream)
@@ -524,6 +529,8 @@ def main():
         }
         line["config"]["schedule"] = schedule
         line["config"]["combine"] = combine
+        if args.no_l2_flush:
+            line["config"]["l2"] = "NOT flushed between steps (diagnostic run; not a contract number)"
         if nvlink is not None:
             line["nvlink"] = nvlink
         if verified is not None:
