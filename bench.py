@@ -634,9 +634,9 @@ def histogram_main(args, rank: int, ws: int):
         sys.exit(3)
 
 
-# DRAM and L2 bytes per launch of the one-launch kernel at world size 1, from the ncu captures
-# summarised under profiles/ (a profiler cannot run inside the timed loop, so the figures are
-# constants of the kernel + workload, re-measured whenever the kernel changes).
+# DRAM and L2 bytes per launch of the one-launch kernel at world size 1, from ncu captures of this
+# kernel on this workload (a profiler cannot run inside the timed loop, so the figures are constants
+# of the kernel + workload, re-measured whenever the kernel changes).
 SINGLE_GPU_TRAFFIC = {
     ("c4", "pipelined", "push"): {"dram_bytes": 5.72e6, "l2_bytes": 37.1e6,
                                   "source": "ncu --set full, pipe_forward_kernel, c4 at world size 1: dram__bytes_read.sum 3.79 MB + "
