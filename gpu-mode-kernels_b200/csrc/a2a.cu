@@ -165,12 +165,15 @@ int check_blobs(const a2a_config& cfg, const uint8_t* all, size_t nbytes, char* 
 }
 
 // Sender blocks of the pipelined kernel.  16-bit payload: one thread per block drives the copy
-// engine with four 14 KB stores in flight, 48 blocks keep about 2.7 MB on the way to the peers
-// (measured at 8 GPUs: the time of the sending role falls as 1/blocks up to there).  FP8: a block
-// quantises a row at a time and the arithmetic is the cost, so more SMs take part.
+// engine (two 14 KB loads ahead, four stores in flight).  Measured at 8 GPUs, the sending role alone
+// takes 52 us + 624 us / blocks (78 / 65 / 63 / 60 us with 24 / 48 / 64 / 96 blocks) and the whole
+// call 126.7 / 113.8 / 110.6 / 109.1 us: 96 blocks at 8 ranks, where there is most to send; 48 below,
+// where the call is a chain of latencies and the expert blocks are better served.  FP8: a block
+// quantises a row at a time and the arithmetic is the cost: 96.
 int pipe_senders(const a2a_config& c) {
     if (c.world_size == 1) return 0;
-    return c.senders > 0 ? c.senders : (c.payload == A2A_PAYLOAD_FP8 ? 96 : 48);
+    if (c.senders > 0) return c.senders;
+    return (c.payload == A2A_PAYLOAD_FP8 || c.world_size >= 8) ? 96 : 48;
 }
 
 int validate(const a2a_config& c) {

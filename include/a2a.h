@@ -86,7 +86,7 @@ typedef struct a2a_config {
     int32_t chunks;          /* phased schedule: token chunks a call is pipelined in, 1..4;
                                 0 selects 1.  Every rank of a group must pass the same value */
     int32_t senders;         /* pipelined schedule: blocks that only move rows; 0 selects 48
-                                (96 with the FP8 payload, whose senders also quantise)       */
+                                (96 at 8 ranks and with the FP8 payload)                     */
 } a2a_config;
 
 /* First error recorded by a kernel since the last a2a_status_clear(). */
