@@ -638,9 +638,9 @@ def histogram_main(args, rank: int, ws: int):
 # kernel on this workload (a profiler cannot run inside the timed loop, so the figures are constants
 # of the kernel + workload, re-measured whenever the kernel changes).
 SINGLE_GPU_TRAFFIC = {
-    ("c4", "pipelined", "push"): {"dram_bytes": 5.72e6, "l2_bytes": 37.1e6,
+    ("c4", "pipelined", "push"): {"dram_bytes": 5.26e6, "l2_bytes": 37.0e6,
                                   "source": "ncu --set full, pipe_forward_kernel, c4 at world size 1: dram__bytes_read.sum 3.79 MB + "
-                                            "dram__bytes_write.sum 1.93 MB; L2 sectors from the SMs 3.95 MB read + 33.2 MB written"},
+                                            "dram__bytes_write.sum 1.46 MB; L2 sectors from the SMs 3.93 MB read + 33.1 MB written"},
     ("c4", "phased", "pull"): {"dram_bytes": 7.76e6, "l2_bytes": 100.2e6,
                                "source": "ncu --set full, forward_kernel (phased schedule), c4 at world size 1: dram__bytes_read.sum "
                                          "4.16 MB + dram__bytes_write.sum 3.60 MB; L2 sectors from the SMs 63.4 MB read + 36.8 MB written"},

@@ -99,6 +99,7 @@ struct a2a_ctx {
     int forward_grid;       // co-resident grid of the one-launch kernel
     int pipe_smem;          // dynamic shared memory of the pipelined kernels
     bool fused;             // a2a_forward uses the one-launch kernel
+    bool plain_launch;      // A2A_LAUNCH=plain: ordinary instead of cooperative launch of the one-launch kernels
     char errmsg[160];       // detail of the last host-detected error
     long long* trace;       // device trace buffer (always allocated, used only while tracing is on)
     int last_grid;          // grid of the most recent traced launch
@@ -284,7 +285,7 @@ int launch(a2a_ctx* c, KernelFn fn, int grid, int smem, cudaStream_t st, bool co
     if (p.trace != nullptr && grid > kTraceBlocks) p.trace = nullptr;
     if (p.trace != nullptr) c->last_grid = grid;
     void* args[] = {&p};
-    cudaError_t e = cooperative
+    cudaError_t e = (cooperative && !c->plain_launch)
         ? cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(kThreads), args, smem, st)
         : cudaLaunchKernel((const void*)fn, dim3(grid), dim3(kThreads), args, smem, st);
     c->launches++;
@@ -521,6 +522,14 @@ int a2a_create(a2a_ctx** out, const a2a_config* cfg) {
     }
     if (e == cudaSuccess) e = cudaDeviceSynchronize();  // memsets done before any peer may write here
     if (e != cudaSuccess) { a2a_destroy(c); return -(int)e; }
+    {
+        // Opt-in, for measurement: launch the one-launch kernels like any other kernel.  The grid is sized
+        // to be co-resident either way, but only the cooperative launch makes the driver GUARANTEE it; with
+        // an ordinary launch a grid that did not get all its blocks running at once ends in
+        // A2A_ERR_TIMEOUT (every wait is bounded), not in a hang.
+        const char* env = getenv("A2A_LAUNCH");
+        c->plain_launch = (env != nullptr && strcmp(env, "plain") == 0);
+    }
     c->peers_ready = (cfg->world_size == 1);
     *out = c;
     return A2A_OK;
