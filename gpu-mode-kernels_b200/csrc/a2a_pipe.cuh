@@ -179,24 +179,35 @@ __device__ __forceinline__ void build_send_lists(const DevParams& p, const Sende
 // A sender thread's destinations whose last store has been issued but not yet waited for, oldest
 // first.  Bulk groups complete in order, so destination d (last group g_d) is through once at most
 // (groups committed since g_d) groups are pending.  Nothing is waited for at a destination boundary:
-// a destination is booked `kArrivalLag` stores later, or at the end -- with one row per destination
-// (small batches) all rows leave back to back and one wait at the end covers them.
+// a destination is booked when its last store is `kArrivalLag` stores or `kArrivalAgeNs` old --
+// by then the peer has acknowledged it, or nearly -- or at the end.  With one row per destination
+// (small batches, many sender blocks) all rows leave back to back, and no flag waits for stores to
+// OTHER destinations to pile up behind it.
+constexpr long long kArrivalAgeNs = 2500;  // about one loaded NVLink round trip
+
 struct PendingDests {
     int d[A2A_MAX_WORLD];
     long long g[A2A_MAX_WORLD];
+    long long t[A2A_MAX_WORLD];
     int head = 0, tail = 0;
     __device__ __forceinline__ bool empty() const { return head == tail; }
     __device__ __forceinline__ void push(int dest, long long group) {
         d[tail % A2A_MAX_WORLD] = dest;
         g[tail % A2A_MAX_WORLD] = group;
+        t[tail % A2A_MAX_WORLD] = global_ns();
         ++tail;
     }
-    // Book every destination that is at least `lag` groups old (lag 0: all of them); `now` = groups committed so far.
+    // Book every destination that is at least `lag` groups or kArrivalAgeNs old (lag 0: all of them);
+    // `now` = groups committed so far.
     template <typename Arrive>
     __device__ __forceinline__ void drain(long long now, int lag, Arrive arrive) {
-        while (head != tail && now - 1 - g[head % A2A_MAX_WORLD] >= lag) {
-            bulk_wait_done((int)min(now - 1 - g[head % A2A_MAX_WORLD], 5LL));
-            arrive(d[head % A2A_MAX_WORLD]);
+        const long long now_ns = head != tail ? global_ns() : 0;
+        while (head != tail) {
+            const int h = head % A2A_MAX_WORLD;
+            const long long since = now - 1 - g[h];
+            if (since < lag && now_ns - t[h] < kArrivalAgeNs) break;
+            bulk_wait_done((int)min(since, 5LL));
+            arrive(d[h]);
             ++head;
         }
     }
