@@ -292,10 +292,12 @@ int a2a_status_peek(a2a_ctx* ctx);
 /* In-kernel trace.  While enabled, thread 0 of every block stamps the SM cycle counter
  * at each phase boundary of the launches that follow (slot 0 of a block holds the
  * nanosecond global timer at its start; then start, routed (pipelined: the block's role bits),
- * sent, dispatch-seen, expert-done, expert-seen, combine-done; the pipelined kernel also fills
- * slots 8+i / 16+i with "rows of the i-th source seen / done" and 24+i with "i-th destination
- * finished").  a2a_trace_read synchronises the device and copies the stamps of the most recent
- * traced launch to host memory: `out` must hold max_blocks * 32 int64 (*stamps_per_block
+ * sent, dispatch-seen, expert-done, expert-seen, combine-done; the pipelined kernel also fills,
+ * depending on the block's role, slots 8+i / 16+i with "rows of the i-th source seen / done"
+ * (expert blocks), 24+i with "stores to the i-th destination acknowledged" and 8..10 with
+ * set-up steps (sender blocks), 24..27 with routing steps (router blocks)).  a2a_trace_read
+ * synchronises the device and copies the stamps of the most recent traced launch to host
+ * memory: `out` must hold max_blocks * 32 int64 (*stamps_per_block
  * returns the 32).  Both calls synchronise: keep them
  * off the timed path.  Replaces the profile buffer of the final reference submission
  * (submission_v9.py:117, :162-184, p2p_state_get_profile). */
